@@ -6,18 +6,20 @@ Public entry points: ``Engine`` (the step function), ``LLM`` (generation through
 the scheduler), ``SamplingParams``, and the command line
 ``python -m safetyraise_lmengine_b200 inspect|run|benchmark|replay``.
 """
+from .config import nekedra as _nekedra
 from .config import qwen3 as _qwen3
 from .config.registry import ARCHITECTURES, register_architecture, spec_from_config  # noqa: F401
 from .errors import *  # noqa: F401,F403
 
 
 def _build_decoder(spec, mctx, source):
-    from .parts import attention, block, feedforward, norm, position  # noqa: F401  (register the parts)
+    from . import parts  # noqa: F401  (importing the package registers the parts)
     from .parts.model import DecoderModel
     return DecoderModel(spec, mctx, source)
 
 
 register_architecture(_qwen3.ARCHITECTURE, _qwen3.read_spec, _build_decoder, _qwen3.adapt_source)
+register_architecture(_nekedra.ARCHITECTURE, _nekedra.read_spec, _build_decoder)
 
 __version__ = "0.1.0"
 

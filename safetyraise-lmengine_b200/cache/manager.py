@@ -34,11 +34,16 @@ class CacheGroupSpec:
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: torch.dtype = torch.float32
+    v_head_dim: Optional[int] = None         # None: values as wide as keys; 0: no value pool; else their own size
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
     def bytes_per_token(self, dtype: torch.dtype) -> int:
         if self.kind == FIXED_STATE:
             return 0
-        return 2 * len(self.entries) * self.kv_heads * self.head_dim * (4 if dtype == torch.float32 else 2)
+        return len(self.entries) * self.kv_heads * (self.head_dim + self.value_dim) * (4 if dtype == torch.float32 else 2)
 
     def bytes_per_request(self, dtype: torch.dtype, context: int, page_size: int = 1) -> int:
         """What one request of ``context`` tokens holds in this group at most: its keys and values (of a
@@ -121,6 +126,8 @@ class CacheManager:
         # device memory: per paged group [entries, 2, num_pages, kv_heads, page_size, head_dim]:
         # one KV head's share of a page is contiguous, which is what the attention kernels stream
         self.kv_pools: Dict[str, torch.Tensor] = {}
+        self.k_pools: Dict[str, torch.Tensor] = {}     # groups whose values are not as wide as their keys
+        self.v_pools: Dict[str, torch.Tensor] = {}
         self.state_pools: Dict[str, torch.Tensor] = {}
         self.entry_home: Dict[int, Tuple[str, int]] = {}
         for g in self.groups:
@@ -133,9 +140,17 @@ class CacheManager:
             if g.kind == FIXED_STATE:
                 self.state_pools[g.name] = torch.zeros((len(g.entries), max_requests) + tuple(g.state_shape),
                                                        dtype=g.state_dtype, device=device)
-            else:
+            elif g.value_dim == g.head_dim:
                 self.kv_pools[g.name] = torch.zeros((len(g.entries), 2, num_pages, g.kv_heads, page_size,
                                                      g.head_dim), dtype=dtype, device=device)
+            else:
+                # keys and values of different sizes: a pool each (no value pool when the values are read
+                # from the keys)
+                self.k_pools[g.name] = torch.zeros((len(g.entries), num_pages, g.kv_heads, page_size, g.head_dim),
+                                                   dtype=dtype, device=device)
+                if g.value_dim:
+                    self.v_pools[g.name] = torch.zeros((len(g.entries), num_pages, g.kv_heads, page_size,
+                                                        g.value_dim), dtype=dtype, device=device)
         self._table_buf = (C.c_int32 * (num_pages + 1))()
 
     def __del__(self):
@@ -218,6 +233,8 @@ class CacheManager:
     def kv_of_entry(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor, str]:
         """(K pool, V pool, group name) of one cache entry: [num_pages, kv_heads, page_size, head_dim]."""
         name, i = self.entry_home[entry]
+        if name in self.k_pools:         # [num_pages, kv_heads, page_size, key size] and [.., value size] (or None)
+            return self.k_pools[name][i], (self.v_pools[name][i] if name in self.v_pools else None), name
         pool = self.kv_pools[name]
         return pool[i, 0], pool[i, 1], name
 

@@ -39,6 +39,8 @@ def register_architecture(name: str, read_spec, build_model, adapt_source=None) 
 
 def architecture_of(config: dict) -> Architecture:
     names = config.get("architectures")
+    if names is None and isinstance(config.get("architecture"), str):     # one name, not in a list
+        names = [config["architecture"]]
     if not isinstance(names, list) or len(names) != 1 or not isinstance(names[0], str):
         raise ConfigError("config.json: 'architectures' must be a list holding exactly one name")
     if names[0] not in ARCHITECTURES:

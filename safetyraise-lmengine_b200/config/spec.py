@@ -73,6 +73,92 @@ class AttentionSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class SinkAttentionNames:
+    """Tensor names of an attention mixer with biases, sinks and value mixing; a bias is its weight's name + ``bias_suffix``."""
+    q: str = "mix.q"
+    k: str = "mix.k"
+    v: str = "mix.v"
+    o: str = "mix.o"
+    sink: str = "mix.sink"
+    value_mix: str = "mix.vmix"
+    bias_suffix: str = ".b"
+
+
+@dataclass(frozen=True)
+class SinkAttentionSpec(MixerSpec):
+    """Grouped-query attention whose keys and values may differ in size, without a position encoding."""
+    hidden_size: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0                       # query / key size
+    v_head_dim: int = 0                     # value size
+    softmax_scale: float = 0.0
+    bias: bool = True                       # q, k and v projections carry biases
+    sink: bool = True                       # one learned term per head in the softmax denominator
+    value_mix: str = ""                     # "": values as projected; "keep": also kept for later layers;
+                                            # "mix": (1 - lambda) v + lambda (the values a "keep" layer kept)
+    window: Optional[int] = None
+    names: SinkAttentionNames = SinkAttentionNames()
+
+
+@dataclass(frozen=True)
+class LatentAttentionNames:
+    q: str = "mix.q"
+    down: str = "mix.dkv"                   # rows: the latent (kv_rank), then the shared rotated key part (rot_dim)
+    latent_norm: str = "mix.dkv.norm"
+    up_k: str = "mix.uk"
+    up_v: str = "mix.uv"
+    gate: str = "mix.g"
+    o: str = "mix.o"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec(MixerSpec):
+    """Attention whose cache holds one normed latent and one rotated key part per token; per-head keys
+    and values are up projections of the latent."""
+    hidden_size: int = 0
+    heads: int = 0
+    head_dim: int = 0                       # unrotated query / key size per head
+    rot_dim: int = 0                        # rotated query / key size per head (the key part is shared by the heads)
+    v_head_dim: int = 0
+    kv_rank: int = 0
+    softmax_scale: float = 0.0
+    position: Optional[PositionSpec] = None  # rotation of the rot_dim part (its first rotary_dim elements)
+    latent_norm_eps: float = 1e-6
+    output_gate: bool = True                # head outputs times sigmoid of a per-head projection of the input
+    names: LatentAttentionNames = LatentAttentionNames()
+
+
+@dataclass(frozen=True)
+class DeltaRuleNames:
+    q: str = "mix.q"
+    k: str = "mix.k"
+    v: str = "mix.v"
+    conv_suffix: str = ".conv"              # the short convolution of a projection: its weight's name + this
+    beta: str = "mix.b"
+    decay: str = "mix.a"
+    decay_log: str = "mix.A_log"
+    decay_bias: str = "mix.dt_bias"
+    out_norm: str = "mix.norm"
+    gate: str = "mix.g"
+    o: str = "mix.o"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec(MixerSpec):
+    """The gated delta rule: a matrix of state per head, written and read token by token."""
+    hidden_size: int = 0
+    heads: int = 0                          # value heads; q / k heads are shared by heads / kv_heads of them
+    kv_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    conv_taps: int = 1
+    norm_eps: float = 1e-6                  # of the per-head norm of the read-out
+    unit_eps: float = 1e-6                  # inside the root that makes q and k unit vectors
+    names: DeltaRuleNames = DeltaRuleNames()
+
+
+@dataclass(frozen=True)
 class FeedForwardSpec:
     kind: str            # registry key in parts.FEED_FORWARDS
     hidden_size: int
@@ -85,12 +171,19 @@ class FeedForwardSpec:
 class LayerSpec:
     block: str                               # registry key in parts.BLOCKS
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]  # None: a layer of a mixer alone (blocks that allow it)
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
     weight_prefix: str                       # e.g. "model.layers.3."
     mixer_norm_name: str = "input_layernorm.weight"              # appended to weight_prefix
     feed_forward_norm_name: str = "post_attention_layernorm.weight"
+    # blocks that also norm a sublayer's result and gate it before it joins the residual stream:
+    mixer_post_norm: Optional[NormSpec] = None
+    feed_forward_post_norm: Optional[NormSpec] = None
+    mixer_post_norm_name: str = "norm1b"
+    feed_forward_post_norm_name: str = "norm2b"
+    mixer_gate_name: str = "rg1"             # weight [hidden, hidden]; its bias: this name + ".b"
+    feed_forward_gate_name: str = "rg2"
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,273 @@
+// Paged causal attention for heads whose keys and values differ in size, float32 arithmetic.
+//
+// What it adds to the attention of equal head sizes:
+//   * dk (query/key size) and dv (value size) are separate; with no value pool the values ARE the
+//     first dv elements of the keys (a cache that holds one latent vector per token serves as both);
+//   * an optional sink per query head: one more term exp(sink) in the softmax denominator, with no
+//     key and no value behind it;
+//   * queries are float32 (they may be the product of a projection folded into them).
+//
+// A block takes 16 rows (tokens x query heads of one KV head) of one entry and walks the keys in
+// blocks of 32 aligned to the start of the sequence; a row's sums depend on its position alone (key
+// blocks that a row does not see leave its running maximum, sum and output bit for bit as they were),
+// so the result is the same however the tokens were cut into steps or batched.
+//
+// Beside it: the kernel that adds the projections' biases, mixes the values with those kept from an
+// earlier layer and appends keys and values to the pages.
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace srlm {
+
+constexpr int kRows = 16, kKeys = 32, kWarps = 4, kRowsPerWarp = kRows / kWarps;
+
+template <typename TC, typename TO, int VPL>
+__global__ void __launch_bounds__(kWarps * 32)
+paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict__ k_cache,
+                               const TC* __restrict__ v_cache, TO* __restrict__ out,
+                               const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
+                               const int* __restrict__ kv_lens, const float* __restrict__ sinks, int nq, int nkv,
+                               int dk, int dv, int page_size, float scale, int window) {
+  extern __shared__ float smem[];
+  const int e = blockIdx.z, kvh = blockIdx.y;
+  const int G = nq / nkv;
+  const int t0 = cu_q[e], q_len = cu_q[e + 1] - t0, kv_len = kv_lens[e];
+  const int rows = q_len * G;
+  const int r0 = blockIdx.x * kRows;
+  if (r0 >= rows) return;
+  const int ks = dk + 1;                                   // padded key row: lanes read different banks
+  float* q_s = smem;                                       // [kRows][dk]
+  float* k_s = q_s + kRows * dk;                           // [kKeys][dk + 1]
+  float* v_s = v_cache ? k_s + kKeys * ks : k_s;           // [kKeys][dv], or the keys' leading part
+  const int vs = v_cache ? dv : ks;
+  float* p_s = k_s + kKeys * ks + (v_cache ? kKeys * dv : 0);   // [kRows][kKeys]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int start = kv_len - q_len;                        // position of the entry's first token of this step
+  const int* table = block_table + (size_t)e * table_stride;
+
+  for (int idx = tid; idx < kRows * dk; idx += blockDim.x) {
+    const int r = idx / dk, d = idx - r * dk, row = r0 + r;
+    q_s[idx] = row < rows ? q[((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dk + d] : 0.f;
+  }
+
+  float m[kRowsPerWarp], l[kRowsPerWarp], acc[kRowsPerWarp][VPL];
+  int pos[kRowsPerWarp], first[kRowsPerWarp];
+#pragma unroll
+  for (int i = 0; i < kRowsPerWarp; ++i) {
+    const int row = r0 + warp * kRowsPerWarp + i;
+    const bool live = row < rows;
+    pos[i] = live ? start + row / G : -1;                  // a row beyond the entry sees no key
+    first[i] = (window > 0 && live) ? max(0, pos[i] - window + 1) : 0;
+    const int h = kvh * G + (live ? row % G : 0);
+    m[i] = sinks ? sinks[h] : -CUDART_INF_F;
+    l[i] = sinks ? 1.f : 0.f;
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) acc[i][c] = 0.f;
+  }
+  const int last_row = min(rows, r0 + kRows) - 1;
+  const int max_pos = start + last_row / G, min_pos = start + r0 / G;
+  const int first_key = window > 0 ? max(0, min_pos - window + 1) : 0;
+
+  for (int jb = (first_key / kKeys) * kKeys; jb <= max_pos; jb += kKeys) {
+    __syncthreads();                                       // the tile of the iteration before is no longer read
+    for (int idx = tid; idx < kKeys * dk; idx += blockDim.x) {
+      const int jj = idx / dk, d = idx - jj * dk, j = jb + jj;
+      float v = 0.f;
+      if (j <= max_pos) {
+        const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
+        v = to_float(k_cache[rowi * dk + d]);
+      }
+      k_s[jj * ks + d] = v;
+    }
+    if (v_cache) {
+      for (int idx = tid; idx < kKeys * dv; idx += blockDim.x) {
+        const int jj = idx / dv, d = idx - jj * dv, j = jb + jj;
+        float v = 0.f;
+        if (j <= max_pos) {
+          const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
+          v = to_float(v_cache[rowi * dv + d]);
+        }
+        v_s[jj * dv + d] = v;
+      }
+    }
+    __syncthreads();
+
+    float dot[kRowsPerWarp];
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; ++i) dot[i] = 0.f;
+    const float* kr = k_s + lane * ks;
+    const float* qr = q_s + warp * kRowsPerWarp * dk;
+    for (int d = 0; d < dk; ++d) {
+      const float kv = kr[d];
+#pragma unroll
+      for (int i = 0; i < kRowsPerWarp; ++i) dot[i] += qr[i * dk + d] * kv;
+    }
+    const int j = jb + lane;
+#pragma unroll
+    for (int i = 0; i < kRowsPerWarp; ++i) {
+      const bool valid = j <= pos[i] && j >= first[i];
+      const float s = valid ? dot[i] * scale : -CUDART_INF_F;
+      const float m_new = fmaxf(m[i], warp_max(s));
+      float alpha = 1.f, p = 0.f;
+      if (m_new != -CUDART_INF_F) {                        // else: nothing seen yet, nothing to rescale
+        alpha = expf(m[i] - m_new);
+        p = valid ? expf(s - m_new) : 0.f;
+      }
+      l[i] = l[i] * alpha + warp_sum(p);
+      m[i] = m_new;
+#pragma unroll
+      for (int c = 0; c < VPL; ++c) acc[i][c] *= alpha;
+      p_s[(warp * kRowsPerWarp + i) * kKeys + lane] = p;
+    }
+    __syncwarp();
+    const int n_here = min(kKeys, max_pos - jb + 1);
+    for (int jj = 0; jj < n_here; ++jj) {
+      float pj[kRowsPerWarp];
+#pragma unroll
+      for (int i = 0; i < kRowsPerWarp; ++i) pj[i] = p_s[(warp * kRowsPerWarp + i) * kKeys + jj];
+      const float* vr = v_s + jj * vs;
+#pragma unroll
+      for (int c = 0; c < VPL; ++c) {
+        const int col = lane + 32 * c;
+        const float v = col < dv ? vr[col] : 0.f;
+#pragma unroll
+        for (int i = 0; i < kRowsPerWarp; ++i) acc[i][c] += pj[i] * v;
+      }
+    }
+    __syncwarp();
+  }
+
+#pragma unroll
+  for (int i = 0; i < kRowsPerWarp; ++i) {
+    const int row = r0 + warp * kRowsPerWarp + i;
+    if (row >= rows) continue;
+    const float inv = 1.f / l[i];
+    TO* o = out + ((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dv;
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) {
+      const int col = lane + 32 * c;
+      if (col < dv) o[col] = from_float<TO>(acc[i][c] * inv);
+    }
+  }
+}
+
+// One block per token: q = projection + bias into its own buffer (float32); k and v = projection +
+// bias; mix_mode 1 keeps v (float32, [T, nkv * dv]) for later layers, mix_mode 2 replaces v by
+// (1 - lambda) v + lambda kept; k and the final v go to the pages (kv_slot[t] = page * page_size + offset).
+template <typename TP, typename TC>
+__global__ void attention_bias_append_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ bias,
+                                             float* __restrict__ q_out, TC* __restrict__ k_cache,
+                                             TC* __restrict__ v_cache, const int* __restrict__ kv_slot,
+                                             float* __restrict__ v_keep, const float* __restrict__ lambda,
+                                             int mix_mode, int write_kv, int nq, int nkv, int dk, int dv,
+                                             int page_size) {
+  const int t = blockIdx.x;
+  const TP* p = proj + (size_t)t * ldp;
+  const int nqd = nq * dk, nkd = nkv * dk, nvd = nkv * dv;
+  for (int c = threadIdx.x; c < nqd; c += blockDim.x)
+    q_out[(size_t)t * nqd + c] = to_float(p[c]) + (bias ? bias[c] : 0.f);
+  const int slot = kv_slot[t];
+  const size_t page = slot / page_size, off = slot % page_size;
+  if (write_kv) {
+    for (int c = threadIdx.x; c < nkd; c += blockDim.x) {
+      const int h = c / dk, d = c - h * dk;
+      const float v = to_float(p[nqd + c]) + (bias ? bias[nqd + c] : 0.f);
+      k_cache[((page * nkv + h) * page_size + off) * dk + d] = from_float<TC>(v);
+    }
+  }
+  const float lam = mix_mode == 2 ? lambda[0] : 0.f;
+  for (int c = threadIdx.x; c < nvd; c += blockDim.x) {
+    const int h = c / dv, d = c - h * dv;
+    float v = to_float(p[nqd + nkd + c]) + (bias ? bias[nqd + nkd + c] : 0.f);
+    if (mix_mode == 1) v_keep[(size_t)t * nvd + c] = v;
+    if (mix_mode == 2) v = (1.f - lam) * v + lam * v_keep[(size_t)t * nvd + c];
+    if (write_kv) v_cache[((page * nkv + h) * page_size + off) * dv + d] = from_float<TC>(v);
+  }
+}
+
+template <typename TC, typename TO>
+static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, const float* q, const void* k_cache,
+                          const void* v_cache, void* out, const int* block_table, int table_stride, const int* cu_q,
+                          const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
+                          float scale, int window) {
+#define SRLM_GENERAL_CASE(V)                                                                                   \
+  case V: {                                                                                                    \
+    auto kern = paged_attention_general_kernel<TC, TO, V>;                                                     \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    kern<<<grid, kWarps * 32, smem, stream>>>(q, (const TC*)k_cache, (const TC*)v_cache, (TO*)out, block_table, \
+                                              table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size,  \
+                                              scale, window);                                                  \
+    break;                                                                                                     \
+  }
+  switch (vpl) {
+    SRLM_GENERAL_CASE(1)
+    SRLM_GENERAL_CASE(2)
+    SRLM_GENERAL_CASE(4)
+    SRLM_GENERAL_CASE(8)
+    SRLM_GENERAL_CASE(16)
+  }
+#undef SRLM_GENERAL_CASE
+  return launched();
+}
+
+}  // namespace srlm
+
+using namespace srlm;
+
+// q: float32 [T, nq, dk]; k_cache [pages, nkv, page_size, dk]; v_cache [pages, nkv, page_size, dv] or
+// null (the values are the keys' first dv elements); out [T, nq, dv] in out_dtype; sinks: float32 [nq] or null.
+extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache, const void* v_cache, void* out,
+                                            int cache_dtype, int out_dtype, const int* block_table,
+                                            int table_stride, const int* cu_q, const int* kv_lens,
+                                            const float* sinks, int n_entries, int max_q_len, int nq, int nkv,
+                                            int dk, int dv, int page_size, float scale, int window,
+                                            cudaStream_t stream) {
+  if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  if (nq <= 0 || nkv <= 0 || nq % nkv || dk <= 0 || dv <= 0 || dv > 512 || page_size <= 0 || (!v_cache && dv > dk))
+    return refuse(ST_BAD_SIZE, "paged_attention_general: nq=%d nkv=%d dk=%d dv=%d page_size=%d (dv <= 512; values "
+                  "read from the keys need dv <= dk)", nq, nkv, dk, dv, page_size);
+  if (n_entries > 65535 || nkv > 65535) return refuse(ST_BAD_SIZE, "paged_attention_general: %d entries", n_entries);
+  const size_t smem = ((size_t)kRows * dk + (size_t)kKeys * (dk + 1) + (v_cache ? (size_t)kKeys * dv : 0) +
+                       (size_t)kRows * kKeys) * sizeof(float);
+  if (smem > 220 * 1024) return refuse(ST_BAD_SIZE, "paged_attention_general: dk=%d dv=%d need %zu bytes of shared memory", dk, dv, smem);
+  const int G = nq / nkv;
+  const long long tiles = ((long long)max_q_len * G + kRows - 1) / kRows;
+  dim3 grid((unsigned)tiles, (unsigned)nkv, (unsigned)n_entries);
+  int vpl = 1;
+  while (vpl * 32 < dv) vpl <<= 1;
+  if (cache_dtype == DT_F32 && out_dtype == DT_F32)
+    return launch_general<float, float>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
+                                        cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window);
+  if (cache_dtype == DT_BF16 && out_dtype == DT_F32)
+    return launch_general<bf16, float>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
+                                       cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window);
+  if (cache_dtype == DT_BF16 && out_dtype == DT_BF16)
+    return launch_general<bf16, bf16>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
+                                      cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window);
+  return refuse(ST_BAD_DTYPE, "paged_attention_general: cache dtype %d with output dtype %d", cache_dtype, out_dtype);
+}
+
+// proj: [T, ldp] in proj_dtype, columns q (nq * dk), k (nkv * dk), v (nkv * dv); bias: float32 over the
+// same columns or null.  mix_mode 0: v as it is; 1: also kept in v_keep; 2: mixed with v_keep by lambda[0].
+extern "C" int srlm_attention_bias_append(const void* proj, int proj_dtype, long long ldp, const float* bias,
+                                          float* q_out, void* k_cache, void* v_cache, int cache_dtype,
+                                          const int* kv_slot, float* v_keep, const float* lambda, int mix_mode,
+                                          int write_kv, int T, int nq, int nkv, int dk, int dv, int page_size,
+                                          cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (nq <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || page_size <= 0 || ldp < (long long)nq * dk + (long long)nkv * (dk + dv) ||
+      (mix_mode != 0 && !v_keep) || (mix_mode == 2 && !lambda) || mix_mode < 0 || mix_mode > 2)
+    return refuse(ST_BAD_SIZE, "attention_bias_append: nq=%d nkv=%d dk=%d dv=%d ldp=%lld mix_mode=%d", nq, nkv, dk, dv,
+                  ldp, mix_mode);
+#define SRLM_APPEND(TP, TC)                                                                                       \
+  attention_bias_append_kernel<TP, TC><<<T, 256, 0, stream>>>((const TP*)proj, ldp, bias, q_out, (TC*)k_cache,    \
+                                                              (TC*)v_cache, kv_slot, v_keep, lambda, mix_mode,   \
+                                                              write_kv, nq, nkv, dk, dv, page_size)
+  if (proj_dtype == DT_F32 && cache_dtype == DT_F32) SRLM_APPEND(float, float);
+  else if (proj_dtype == DT_F32 && cache_dtype == DT_BF16) SRLM_APPEND(float, bf16);
+  else if (proj_dtype == DT_BF16 && cache_dtype == DT_BF16) SRLM_APPEND(bf16, bf16);
+  else return refuse(ST_BAD_DTYPE, "attention_bias_append: projection dtype %d with cache dtype %d", proj_dtype, cache_dtype);
+#undef SRLM_APPEND
+  return launched();
+}

@@ -1,0 +1,257 @@
+// The gated delta rule: a recurrent mixer with one matrix of state S [dk, dv] per head and request.
+//
+//   S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q            (in this order, per token)
+//
+// with q and k unit vectors per head (q also times dk^-1/2), both and v behind a short causal
+// convolution over time and SiLU, beta = sigmoid(.), g = exp(-exp(A) softplus(a + dt)).  Everything
+// behind the projections is float32.  A request's fixed-size state, one float32 vector per slot:
+//   [ S of every head, stored [head][dv][dk] | the last taps-1 inputs of every convolved channel, [channel][taps-1] ].
+//
+// Four kernels per step:
+//   delta_prepare      -- convolution (reading the slot's last inputs for the first tokens of an entry),
+//                         SiLU, unit norms, beta and g, for all tokens in parallel;
+//   delta_conv_carry   -- the slot's last taps-1 inputs after this step;
+//   delta_recurrence   -- the recurrence, token by token within an entry, entries / heads / columns of S in parallel;
+//   delta_output       -- per head o / rms(o) * w * silu(gate) in the activation dtype.
+// Projection row (proj, [T, ldp]): q (G dk) | k (G dk) | v (H dv) | b (H) | a (H) | gate (H dv).
+#include "common.cuh"
+
+namespace srlm {
+
+constexpr int kMaxTaps = 8;
+constexpr int kLanesPerColumn = 8;       // lanes that share one column of S, each with every 8th row
+constexpr int kColumnsPerBlock = 32;
+
+template <typename TP>
+__global__ void delta_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ conv_w,
+                                     const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                     const float* __restrict__ state, long long state_stride,
+                                     const int* __restrict__ entry_of_token, const int* __restrict__ cu_q,
+                                     const int* __restrict__ slots, float* __restrict__ qkv_out,
+                                     float* __restrict__ beta_out, float* __restrict__ decay_out, int H, int G, int dk,
+                                     int dv, int taps, float unit_eps) {
+  extern __shared__ float ch[];                              // [C] convolved and activated channels of this token
+  const int t = blockIdx.x;
+  const int C = 2 * G * dk + H * dv;
+  const int e = entry_of_token[t];
+  const int local = t - cu_q[e];                             // index of the token among the entry's tokens of this step
+  const float* carry = state + (size_t)slots[e] * state_stride + (size_t)H * dk * dv;   // [C][taps - 1]
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float y = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;                         // the last column weighs the current token
+      const float x = back <= local ? to_float(proj[(size_t)(t - back) * ldp + c])
+                                    : carry[(size_t)c * (taps - 1) + (taps - 1) + (local - back)];
+      y += conv_w[(size_t)c * taps + j] * x;
+    }
+    ch[c] = y / (1.f + expf(-y));
+  }
+  __syncthreads();
+  // unit vectors: a warp per head of q and of k
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int hh = warp; hh < 2 * G; hh += nwarps) {
+    float* v = ch + (size_t)hh * dk;
+    float ss = 0.f;
+    for (int d = lane; d < dk; d += 32) ss += v[d] * v[d];
+    ss = warp_sum(ss);
+    float inv = 1.0f / sqrtf(ss + unit_eps);
+    if (hh < G) inv *= 1.0f / sqrtf((float)dk);
+    for (int d = lane; d < dk; d += 32) v[d] *= inv;
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += blockDim.x) qkv_out[(size_t)t * C + c] = ch[c];
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const float b = to_float(proj[(size_t)t * ldp + C + h]);
+    const float a = to_float(proj[(size_t)t * ldp + C + H + h]) + dt_bias[h];
+    const float sp = a > 20.f ? a : log1pf(expf(a));
+    beta_out[(size_t)t * H + h] = 1.f / (1.f + expf(-b));
+    decay_out[(size_t)t * H + h] = expf(-expf(a_log[h]) * sp);
+  }
+}
+
+// One thread per (entry, channel): the last taps-1 inputs of the channel after this step, taken from the
+// step's tokens and, where the step brought fewer than taps-1, from what the slot held.
+template <typename TP>
+__global__ void delta_conv_carry_kernel(const TP* __restrict__ proj, long long ldp, float* __restrict__ state,
+                                        long long state_stride, long long carry_off, const int* __restrict__ cu_q,
+                                        const int* __restrict__ slots, int n_entries, int C, int taps) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n_entries * C) return;
+  const int e = (int)(i / C), c = (int)(i % C);
+  const int t0 = cu_q[e], n = cu_q[e + 1] - t0, keep = taps - 1;
+  float* carry = state + (size_t)slots[e] * state_stride + carry_off + (size_t)c * keep;
+  float fresh[kMaxTaps];
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) {
+    if (k >= keep) break;
+    const int rel = n - keep + k;                            // index among the step's tokens; negative: held before
+    fresh[k] = rel >= 0 ? to_float(proj[(size_t)(t0 + rel) * ldp + c]) : carry[keep + rel];
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxTaps; ++k) {
+    if (k >= keep) break;
+    carry[k] = fresh[k];
+  }
+}
+
+// Block: 32 columns of one head's S for one entry; a column is shared by 8 lanes, lane l holding rows
+// l, l + 8, ... (RPL of them).  The next token's operands are fetched while this token's are used.
+template <int RPL>
+__global__ void __launch_bounds__(kColumnsPerBlock* kLanesPerColumn)
+delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
+                        float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
+                        const int* __restrict__ slots, float* __restrict__ o_out, int H, int G, int dk, int dv) {
+  const int e = blockIdx.z, h = blockIdx.y;
+  const int col = blockIdx.x * kColumnsPerBlock + threadIdx.x / kLanesPerColumn;
+  const int l = threadIdx.x % kLanesPerColumn;
+  const bool live = col < dv;
+  const int kh = h / (H / G);
+  const int C = 2 * G * dk + H * dv;
+  const int t0 = cu_q[e], t1 = cu_q[e + 1];
+  float* S_col = state + (size_t)slots[e] * state_stride + ((size_t)h * dv + (live ? col : 0)) * dk;
+  float S[RPL], kc[RPL], qc[RPL], kn[RPL], qn[RPL];
+#pragma unroll
+  for (int i = 0; i < RPL; ++i) {
+    const int r = l + kLanesPerColumn * i;
+    S[i] = (live && r < dk) ? S_col[r] : 0.f;
+    kn[i] = qn[i] = 0.f;
+  }
+  float vc, bc, gc, vn = 0.f, bn = 0.f, gn = 0.f;
+#define SRLM_DELTA_FETCH(t)                                                          \
+  do {                                                                               \
+    const float* row = qkv + (size_t)(t) * C;                                        \
+    _Pragma("unroll") for (int i = 0; i < RPL; ++i) {                                \
+      const int r = l + kLanesPerColumn * i;                                         \
+      qn[i] = r < dk ? row[(size_t)kh * dk + r] : 0.f;                               \
+      kn[i] = r < dk ? row[(size_t)(G + kh) * dk + r] : 0.f;                         \
+    }                                                                                \
+    vn = live ? row[(size_t)2 * G * dk + (size_t)h * dv + col] : 0.f;                \
+    bn = beta[(size_t)(t) * H + h];                                                  \
+    gn = decay[(size_t)(t) * H + h];                                                 \
+  } while (0)
+  if (t0 < t1) SRLM_DELTA_FETCH(t0);
+  for (int t = t0; t < t1; ++t) {
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) { kc[i] = kn[i]; qc[i] = qn[i]; }
+    vc = vn; bc = bn; gc = gn;
+    if (t + 1 < t1) SRLM_DELTA_FETCH(t + 1);
+    float ks = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      S[i] *= gc;
+      ks += kc[i] * S[i];
+    }
+    ks += __shfl_xor_sync(0xffffffffu, ks, 1);
+    ks += __shfl_xor_sync(0xffffffffu, ks, 2);
+    ks += __shfl_xor_sync(0xffffffffu, ks, 4);
+    const float u = bc * (vc - ks);
+    float o = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      S[i] += kc[i] * u;
+      o += qc[i] * S[i];
+    }
+    o += __shfl_xor_sync(0xffffffffu, o, 1);
+    o += __shfl_xor_sync(0xffffffffu, o, 2);
+    o += __shfl_xor_sync(0xffffffffu, o, 4);
+    if (live && l == 0) o_out[((size_t)t * H + h) * dv + col] = o;
+  }
+#undef SRLM_DELTA_FETCH
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      const int r = l + kLanesPerColumn * i;
+      if (r < dk) S_col[r] = S[i];
+    }
+  }
+}
+
+// One block per token, a warp per head: o / sqrt(mean(o^2) + eps) * w * silu(gate).
+template <typename TP, typename TA>
+__global__ void delta_output_kernel(const float* __restrict__ o, const float* __restrict__ norm_w, float eps,
+                                    const TP* __restrict__ proj, long long ldp, int gate_off, TA* __restrict__ out,
+                                    int H, int dv) {
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < H; h += nwarps) {
+    const float* row = o + ((size_t)t * H + h) * dv;
+    float ss = 0.f;
+    for (int d = lane; d < dv; d += 32) ss += row[d] * row[d];
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+    for (int d = lane; d < dv; d += 32) {
+      const float z = to_float(proj[(size_t)t * ldp + gate_off + (size_t)h * dv + d]);
+      out[((size_t)t * H + h) * dv + d] = from_float<TA>(row[d] * inv * norm_w[d] * (z / (1.f + expf(-z))));
+    }
+  }
+}
+
+}  // namespace srlm
+
+using namespace srlm;
+
+static int delta_sizes_ok(int H, int G, int dk, int dv, int taps) {
+  return H > 0 && G > 0 && H % G == 0 && dk > 0 && dk <= 256 && dv > 0 && taps >= 1 && taps <= kMaxTaps;
+}
+
+extern "C" int srlm_delta_prepare(const void* proj, int proj_dtype, long long ldp, const float* conv_w,
+                                  const float* a_log, const float* dt_bias, float* state, long long state_stride,
+                                  const int* entry_of_token, const int* cu_q, const int* slots, int n_entries,
+                                  float* qkv_out, float* beta_out, float* decay_out, int T, int H, int G, int dk,
+                                  int dv, int taps, float unit_eps, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  const long long C = 2LL * G * dk + (long long)H * dv;
+  if (!delta_sizes_ok(H, G, dk, dv, taps) || ldp < C + 2LL * H + (long long)H * dv || C * 4 > 200 * 1024 ||
+      state_stride < (long long)H * dk * dv + C * (taps - 1))
+    return refuse(ST_BAD_SIZE, "delta_prepare: H=%d G=%d dk=%d dv=%d taps=%d ldp=%lld state=%lld (dk <= 256, taps <= %d)",
+                  H, G, dk, dv, taps, ldp, state_stride, kMaxTaps);
+  const size_t smem = (size_t)C * sizeof(float);
+  SRLM_DISPATCH_ACT(proj_dtype, TP, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(delta_prepare_kernel<TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    delta_prepare_kernel<TP><<<T, 256, smem, stream>>>((const TP*)proj, ldp, conv_w, a_log, dt_bias, state, state_stride,
+                                                       entry_of_token, cu_q, slots, qkv_out, beta_out, decay_out, H, G,
+                                                       dk, dv, taps, unit_eps);
+    if (taps > 1) {
+      const long long n = (long long)n_entries * C;
+      delta_conv_carry_kernel<TP><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+          (const TP*)proj, ldp, state, state_stride, (long long)H * dk * dv, cu_q, slots, n_entries, (int)C, taps);
+    }
+  });
+  return launched();
+}
+
+extern "C" int srlm_delta_recurrence(const float* qkv, const float* beta, const float* decay, float* state,
+                                     long long state_stride, const int* cu_q, const int* slots, int n_entries,
+                                     float* o_out, int H, int G, int dk, int dv, cudaStream_t stream) {
+  if (n_entries <= 0) return ST_OK;
+  if (!delta_sizes_ok(H, G, dk, dv, 1) || n_entries > 65535 || H > 65535)
+    return refuse(ST_BAD_SIZE, "delta_recurrence: H=%d G=%d dk=%d dv=%d entries=%d (dk <= 256)", H, G, dk, dv, n_entries);
+  dim3 grid((dv + kColumnsPerBlock - 1) / kColumnsPerBlock, H, n_entries);
+  const int threads = kColumnsPerBlock * kLanesPerColumn;
+  const int rpl = (dk + kLanesPerColumn - 1) / kLanesPerColumn;
+#define SRLM_DELTA_CASE(R)                                                                                            \
+  delta_recurrence_kernel<R><<<grid, threads, 0, stream>>>(qkv, beta, decay, state, state_stride, cu_q, slots, o_out, \
+                                                           H, G, dk, dv)
+  if (rpl <= 4) SRLM_DELTA_CASE(4);
+  else if (rpl <= 8) SRLM_DELTA_CASE(8);
+  else if (rpl <= 16) SRLM_DELTA_CASE(16);
+  else SRLM_DELTA_CASE(32);
+#undef SRLM_DELTA_CASE
+  return launched();
+}
+
+extern "C" int srlm_delta_output(const float* o, const float* norm_w, float eps, const void* proj, int proj_dtype,
+                                 long long ldp, int gate_off, void* out, int out_dtype, int T, int H, int dv,
+                                 cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (H <= 0 || dv <= 0 || !(eps > 0.f) || gate_off < 0 || ldp < gate_off + (long long)H * dv)
+    return refuse(ST_BAD_SIZE, "delta_output: H=%d dv=%d gate_off=%d ldp=%lld", H, dv, gate_off, ldp);
+  const int threads = 32 * (H < 8 ? H : 8);
+#define SRLM_DELTA_OUT(TP, TA)                                                                                    \
+  delta_output_kernel<TP, TA><<<T, threads, 0, stream>>>(o, norm_w, eps, (const TP*)proj, ldp, gate_off, (TA*)out, H, dv)
+  if (proj_dtype == DT_F32 && out_dtype == DT_F32) SRLM_DELTA_OUT(float, float);
+  else if (proj_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_DELTA_OUT(float, bf16);
+  else if (proj_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_DELTA_OUT(bf16, bf16);
+  else return refuse(ST_BAD_DTYPE, "delta_output: projection dtype %d with output dtype %d", proj_dtype, out_dtype);
+#undef SRLM_DELTA_OUT
+  return launched();
+}

@@ -1,0 +1,181 @@
+// Attention over a cached latent: the pages hold, per token, one vector c of `rank` elements (the
+// RMS-normed down projection) followed by one rotated key part of `rot` elements shared by all heads.
+// Per head the unrotated key would be U_k c and the value U_v c; neither is ever formed:
+//
+//   score(i, j) = (q_i . U_k c_j + qr_i . kr_j) * scale = ((U_k^T q_i) . c_j + qr_i . kr_j) * scale
+//   out_i       = U_v sum_j p_ij c_j
+//
+// so the attention itself runs with one KV head whose keys are [c, kr] and whose values are the keys'
+// first `rank` elements (paged_attention_general), between the three kernels of this file:
+//   latent_append  -- norm of c, rotation of kr, append to the pages;
+//   latent_absorb  -- per head [U_k^T q | rotated qr] as float32 queries of size rank + rot;
+//   latent_expand  -- per head U_v (sum p c), times the sigmoid of the head's output gate.
+// Rotation: element pairs (2i, 2i + 1), i < pairs, by the step's cos / sin tables [T, pairs]; the rest
+// of the rotated part passes unchanged.  All arithmetic float32.
+#include "common.cuh"
+
+namespace srlm {
+
+constexpr int kTokTile = 16;
+
+// One block per token.  proj row: [.. | c_raw (rank) | kr_raw (rot) | ..] starting at column c_off.
+template <typename TP, typename TC>
+__global__ void latent_append_kernel(const TP* __restrict__ proj, long long ldp, int c_off,
+                                     const float* __restrict__ norm_w, float eps, const float* __restrict__ cos_t,
+                                     const float* __restrict__ sin_t, int pairs, TC* __restrict__ cache,
+                                     const int* __restrict__ kv_slot, int rank, int rot) {
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const TP* p = proj + (size_t)t * ldp + c_off;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const float v = to_float(p[i]);
+    ss += v * v;
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)rank + eps);
+  TC* row = cache + (size_t)kv_slot[t] * (rank + rot);      // one KV head: the flat slot is the row
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) row[i] = from_float<TC>(to_float(p[i]) * inv * norm_w[i]);
+  for (int i = threadIdx.x; i < rot; i += blockDim.x) {
+    float v = to_float(p[rank + i]);
+    if (i < 2 * pairs) {
+      const float c = cos_t[(size_t)t * pairs + (i >> 1)], s = sin_t[(size_t)t * pairs + (i >> 1)];
+      const float other = to_float(p[rank + (i ^ 1)]);
+      v = (i & 1) ? v * c + other * s : v * c - other * s;
+    }
+    row[rank + i] = from_float<TC>(v);
+  }
+}
+
+// Block (token tile, head).  q row: heads x [dim unrotated | rot rotated].  uk: [heads, dim, rank].
+// q_out: float32 [T, heads, rank + rot].
+template <typename TP, typename TW>
+__global__ void latent_absorb_kernel(const TP* __restrict__ proj, long long ldp, const TW* __restrict__ uk,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairs,
+                                     float* __restrict__ q_out, int T, int heads, int dim, int rot, int rank) {
+  extern __shared__ float q_s[];                             // [kTokTile][dim]
+  const int t0 = blockIdx.x * kTokTile, h = blockIdx.y;
+  const int n = min(kTokTile, T - t0);
+  for (int idx = threadIdx.x; idx < kTokTile * dim; idx += blockDim.x) {
+    const int tt = idx / dim, d = idx - tt * dim;
+    q_s[idx] = tt < n ? to_float(proj[(size_t)(t0 + tt) * ldp + (size_t)h * (dim + rot) + d]) : 0.f;
+  }
+  __syncthreads();
+  const int qd = rank + rot;
+  const TW* w = uk + (size_t)h * dim * rank;
+  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
+    float acc[kTokTile];
+#pragma unroll
+    for (int tt = 0; tt < kTokTile; ++tt) acc[tt] = 0.f;
+    for (int d = 0; d < dim; ++d) {
+      const float wv = to_float(w[(size_t)d * rank + r]);
+#pragma unroll
+      for (int tt = 0; tt < kTokTile; ++tt) acc[tt] += q_s[tt * dim + d] * wv;
+    }
+    for (int tt = 0; tt < n; ++tt) q_out[((size_t)(t0 + tt) * heads + h) * qd + r] = acc[tt];
+  }
+  for (int idx = threadIdx.x; idx < n * rot; idx += blockDim.x) {
+    const int tt = idx / rot, i = idx - tt * rot, t = t0 + tt;
+    const TP* src = proj + (size_t)t * ldp + (size_t)h * (dim + rot) + dim;
+    float v = to_float(src[i]);
+    if (i < 2 * pairs) {
+      const float c = cos_t[(size_t)t * pairs + (i >> 1)], s = sin_t[(size_t)t * pairs + (i >> 1)];
+      const float other = to_float(src[i ^ 1]);
+      v = (i & 1) ? v * c + other * s : v * c - other * s;
+    }
+    q_out[((size_t)t * heads + h) * qd + rank + i] = v;
+  }
+}
+
+// Block (token tile, head).  o_lat: float32 [T, heads, rank]; uv_t: [heads, rank, dv] (the up projection
+// of the values, transposed per head); gate: column g_off + h of the projection row, or none.
+template <typename TP, typename TW, typename TA>
+__global__ void latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ uv_t,
+                                     const TP* __restrict__ proj, long long ldp, int g_off, TA* __restrict__ out,
+                                     int T, int heads, int rank, int dv) {
+  extern __shared__ float o_s[];                             // [kTokTile][rank]
+  const int t0 = blockIdx.x * kTokTile, h = blockIdx.y;
+  const int n = min(kTokTile, T - t0);
+  for (int idx = threadIdx.x; idx < kTokTile * rank; idx += blockDim.x) {
+    const int tt = idx / rank, r = idx - tt * rank;
+    o_s[idx] = tt < n ? o_lat[((size_t)(t0 + tt) * heads + h) * rank + r] : 0.f;
+  }
+  __syncthreads();
+  const TW* w = uv_t + (size_t)h * rank * dv;
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    float acc[kTokTile];
+#pragma unroll
+    for (int tt = 0; tt < kTokTile; ++tt) acc[tt] = 0.f;
+    for (int r = 0; r < rank; ++r) {
+      const float wv = to_float(w[(size_t)r * dv + j]);
+#pragma unroll
+      for (int tt = 0; tt < kTokTile; ++tt) acc[tt] += o_s[tt * rank + r] * wv;
+    }
+    for (int tt = 0; tt < n; ++tt) {
+      float g = 1.f;
+      if (g_off >= 0) g = 1.f / (1.f + expf(-to_float(proj[(size_t)(t0 + tt) * ldp + g_off + h])));
+      out[((size_t)(t0 + tt) * heads + h) * dv + j] = from_float<TA>(acc[tt] * g);
+    }
+  }
+}
+
+}  // namespace srlm
+
+using namespace srlm;
+
+#define SRLM_LATENT_TYPES(pd, wd, ...)                                                                     \
+  do {                                                                                                     \
+    if ((pd) == DT_F32 && (wd) == DT_F32) { using TP = float; using TW = float; __VA_ARGS__; }             \
+    else if ((pd) == DT_F32 && (wd) == DT_BF16) { using TP = float; using TW = bf16; __VA_ARGS__; }        \
+    else if ((pd) == DT_BF16 && (wd) == DT_BF16) { using TP = bf16; using TW = bf16; __VA_ARGS__; }        \
+    else return refuse(ST_BAD_DTYPE, "latent attention: projection dtype %d with weight or cache dtype %d", \
+                       (int)(pd), (int)(wd));                                                               \
+  } while (0)
+
+extern "C" int srlm_latent_append(const void* proj, int proj_dtype, long long ldp, int c_off, const float* norm_w,
+                                  float eps, const float* cos_t, const float* sin_t, int pairs, void* cache,
+                                  int cache_dtype, const int* kv_slot, int T, int rank, int rot, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (rank <= 0 || rot < 0 || 2 * pairs > rot || c_off < 0 || ldp < c_off + rank + rot || !(eps > 0.f) ||
+      (pairs > 0 && (!cos_t || !sin_t)))
+    return refuse(ST_BAD_SIZE, "latent_append: rank=%d rot=%d pairs=%d c_off=%d ldp=%lld", rank, rot, pairs, c_off, ldp);
+  SRLM_LATENT_TYPES(proj_dtype, cache_dtype, (latent_append_kernel<TP, TW><<<T, 128, 0, stream>>>(
+      (const TP*)proj, ldp, c_off, norm_w, eps, cos_t, sin_t, pairs, (TW*)cache, kv_slot, rank, rot)));
+  return launched();
+}
+
+extern "C" int srlm_latent_absorb(const void* proj, int proj_dtype, long long ldp, const void* uk, int w_dtype,
+                                  const float* cos_t, const float* sin_t, int pairs, float* q_out, int T, int heads,
+                                  int dim, int rot, int rank, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  const size_t smem = (size_t)kTokTile * dim * sizeof(float);
+  if (heads <= 0 || heads > 65535 || dim <= 0 || rank <= 0 || rot < 0 || 2 * pairs > rot || smem > 48 * 1024 ||
+      ldp < (long long)heads * (dim + rot) || (pairs > 0 && (!cos_t || !sin_t)))
+    return refuse(ST_BAD_SIZE, "latent_absorb: heads=%d dim=%d rot=%d rank=%d pairs=%d ldp=%lld", heads, dim, rot, rank,
+                  pairs, ldp);
+  dim3 grid((T + kTokTile - 1) / kTokTile, heads);
+  SRLM_LATENT_TYPES(proj_dtype, w_dtype, (latent_absorb_kernel<TP, TW><<<grid, 128, smem, stream>>>(
+      (const TP*)proj, ldp, (const TW*)uk, cos_t, sin_t, pairs, q_out, T, heads, dim, rot, rank)));
+  return launched();
+}
+
+extern "C" int srlm_latent_expand(const float* o_lat, const void* uv_t, int w_dtype, const void* proj, int proj_dtype,
+                                  long long ldp, int g_off, void* out, int out_dtype, int T, int heads, int rank,
+                                  int dv, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  const size_t smem = (size_t)kTokTile * rank * sizeof(float);
+  if (heads <= 0 || heads > 65535 || rank <= 0 || dv <= 0 || smem > 200 * 1024 || (g_off >= 0 && ldp < g_off + heads))
+    return refuse(ST_BAD_SIZE, "latent_expand: heads=%d rank=%d dv=%d g_off=%d ldp=%lld", heads, rank, dv, g_off, ldp);
+  dim3 grid((T + kTokTile - 1) / kTokTile, heads);
+#define SRLM_EXPAND(TA)                                                                                          \
+  do {                                                                                                           \
+    auto kern = latent_expand_kernel<TP, TW, TA>;                                                                \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
+    kern<<<grid, 128, smem, stream>>>(o_lat, (const TW*)uv_t, (const TP*)proj, ldp, g_off, (TA*)out, T, heads,   \
+                                      rank, dv);                                                                 \
+  } while (0)
+  if (out_dtype == DT_F32) SRLM_LATENT_TYPES(proj_dtype, w_dtype, SRLM_EXPAND(float));
+  else if (out_dtype == DT_BF16) SRLM_LATENT_TYPES(proj_dtype, w_dtype, SRLM_EXPAND(bf16));
+  else return refuse(ST_BAD_DTYPE, "latent_expand: output dtype %d", out_dtype);
+#undef SRLM_EXPAND
+  return launched();
+}

@@ -737,6 +737,100 @@ class KernelLibrary:
             self.paged_attention_rows(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work_list(64),
                                       nq, nkv, hd, page_size, scale, window)
 
+    # ---- blocks that norm on both sides of a sublayer --------------------------------
+    def gated_postnorm_add(self, residual, sub, gate, gate_bias, post_w, eps, next_w=None, next_eps=0.0,
+                           next_out=None):
+        """residual += post_w * rms_norm(sub * sigmoid(gate + gate_bias)); with next_out also
+        next_out = next_w * rms_norm(residual).  residual float32 [T, H]; sub, gate (may be None) and
+        next_out in the activation dtype; the weights float32 [H]."""
+        T, H = residual.shape
+        if residual.dtype != torch.float32 or tuple(sub.shape) != (T, H) or (gate is not None and gate.dtype != sub.dtype):
+            raise ShapeError(f"gated_postnorm_add: residual {tuple(residual.shape)} {residual.dtype}, sub {tuple(sub.shape)}")
+        self._check(self.lib.srlm_gated_postnorm_add(
+            _ptr(residual), _ptr(sub), _ptr(gate), _ptr(gate_bias), _ptr(post_w), C.c_float(eps), _ptr(next_w),
+            C.c_float(next_eps), _ptr(next_out), dtype_code(sub.dtype), C.c_int(T), C.c_int(H), _stream()),
+            "gated_postnorm_add")
+
+    # ---- attention with separate key and value sizes ---------------------------------------
+    def paged_attention_general(self, ctx, q, k_cache, v_cache, out, block_table, sinks, nq, nkv, dk, dv, scale,
+                                window=0):
+        """Causal attention of the batch of ``ctx`` over pages whose keys have dk and whose values have dv
+        elements (v_cache None: the values are the keys' first dv elements).  q float32 [T, nq * dk];
+        k_cache [pages, nkv, page_size, dk]; out [T, nq * dv], float32 or the cache's dtype; sinks float32
+        [nq] or None: one more term exp(sink) in each head's softmax denominator."""
+        if q.dtype != torch.float32:
+            raise ShapeError("paged_attention_general: float32 queries")
+        self._check(self.lib.srlm_paged_attention_general(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), dtype_code(k_cache.dtype), dtype_code(out.dtype),
+            _ptr(block_table), C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks),
+            C.c_int(ctx.n_entries), C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
+            C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), _stream()), "paged_attention_general")
+
+    def attention_bias_append(self, proj, bias, q_out, k_cache, v_cache, kv_slot, nq, nkv, dk, dv, v_keep=None,
+                              lam=None, mix_mode=0, write_kv=True):
+        """From a stacked q | k | v projection [T, >= nq dk + nkv (dk + dv)]: q + bias to q_out (float32), k + bias
+        and v + bias to the pages.  mix_mode 1 also keeps v in v_keep (float32 [T, nkv dv]); mix_mode 2 writes
+        (1 - lam) v + lam v_keep instead of v (lam: float32 [1] on the device)."""
+        T = proj.shape[0]
+        self._check(self.lib.srlm_attention_bias_append(
+            _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(bias), _ptr(q_out), _ptr(k_cache),
+            _ptr(v_cache), dtype_code(k_cache.dtype), _ptr(kv_slot), _ptr(v_keep), _ptr(lam), C.c_int(mix_mode),
+            C.c_int(int(write_kv)), C.c_int(T), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
+            C.c_int(k_cache.shape[2]), _stream()), "attention_bias_append")
+
+    # ---- attention over a cached latent ----------------------------------------------------
+    def latent_append(self, proj, c_off, norm_w, eps, rotation, cache, kv_slot, rank, rot):
+        """cache row of each token = [rms_norm(proj[c_off : c_off + rank]) * norm_w | rotated proj[.. + rot]]."""
+        pairs = rotation.pairs if rotation is not None else 0
+        self._check(self.lib.srlm_latent_append(
+            _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), C.c_int(c_off), _ptr(norm_w),
+            C.c_float(eps), _ptr(rotation.cos if pairs else None), _ptr(rotation.sin if pairs else None),
+            C.c_int(pairs), _ptr(cache), dtype_code(cache.dtype), _ptr(kv_slot), C.c_int(proj.shape[0]),
+            C.c_int(rank), C.c_int(rot), _stream()), "latent_append")
+
+    def latent_absorb(self, proj, uk, rotation, q_out, heads, dim, rot, rank):
+        """q_out float32 [T, heads, rank + rot] = per head [uk_h^T q_h | rotated rest of the head]; uk [heads, dim, rank]."""
+        pairs = rotation.pairs if rotation is not None else 0
+        self._check(self.lib.srlm_latent_absorb(
+            _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(uk), dtype_code(uk.dtype),
+            _ptr(rotation.cos if pairs else None), _ptr(rotation.sin if pairs else None), C.c_int(pairs), _ptr(q_out),
+            C.c_int(proj.shape[0]), C.c_int(heads), C.c_int(dim), C.c_int(rot), C.c_int(rank), _stream()),
+            "latent_absorb")
+
+    def latent_expand(self, o_lat, uv_t, proj, g_off, out, heads, rank, dv):
+        """out [T, heads * dv] = per head (uv_t_h^T o_lat_h) * sigmoid(proj[:, g_off + h]); uv_t [heads, rank, dv];
+        g_off < 0: no gate."""
+        self._check(self.lib.srlm_latent_expand(
+            _ptr(o_lat), _ptr(uv_t), dtype_code(uv_t.dtype), _ptr(proj), dtype_code(proj.dtype),
+            C.c_longlong(proj.stride(0)), C.c_int(g_off), _ptr(out), dtype_code(out.dtype), C.c_int(o_lat.shape[0]),
+            C.c_int(heads), C.c_int(rank), C.c_int(dv), _stream()), "latent_expand")
+
+    # ---- the gated delta rule ------------------------------------------------------------------
+    def delta_prepare(self, ctx, proj, conv_w, a_log, dt_bias, state, qkv_out, beta_out, decay_out, H, G, dk, dv,
+                      taps, unit_eps):
+        """Convolution + SiLU of the q | k | v columns of proj (carrying each slot's last taps-1 inputs in its
+        state), unit vectors, beta and decay for every token; then the slots' carried inputs are renewed.
+        state: float32 [slots, state_size], laid out as csrc/kernels/delta_rule.cu says."""
+        self._check(self.lib.srlm_delta_prepare(
+            _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(conv_w), _ptr(a_log), _ptr(dt_bias),
+            _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.entry_of_token), _ptr(ctx.cu_q), _ptr(ctx.slots),
+            C.c_int(ctx.n_entries), _ptr(qkv_out), _ptr(beta_out), _ptr(decay_out), C.c_int(proj.shape[0]), C.c_int(H),
+            C.c_int(G), C.c_int(dk), C.c_int(dv), C.c_int(taps), C.c_float(unit_eps), _stream()), "delta_prepare")
+        if taps > 1:
+            self.launches += 1
+
+    def delta_recurrence(self, ctx, qkv, beta, decay, state, o_out, H, G, dk, dv):
+        self._check(self.lib.srlm_delta_recurrence(
+            _ptr(qkv), _ptr(beta), _ptr(decay), _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.cu_q),
+            _ptr(ctx.slots), C.c_int(ctx.n_entries), _ptr(o_out), C.c_int(H), C.c_int(G), C.c_int(dk), C.c_int(dv),
+            _stream()), "delta_recurrence")
+
+    def delta_output(self, o, norm_w, eps, proj, gate_off, out, H, dv):
+        self._check(self.lib.srlm_delta_output(
+            _ptr(o), _ptr(norm_w), C.c_float(eps), _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)),
+            C.c_int(gate_off), _ptr(out), dtype_code(out.dtype), C.c_int(o.shape[0]), C.c_int(H), C.c_int(dv),
+            _stream()), "delta_output")
+
     # ---- sampling -------------------------------------------------------------
     def argmax(self, logits, out_tokens, bad_flag):
         n, V = logits.shape

@@ -63,6 +63,8 @@ class CacheNeed:
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: torch.dtype = torch.float32
+    v_head_dim: Optional[int] = None          # None: values as wide as keys; 0: no value pool (the values are
+                                              # read from the keys); else the values' own size
 
 
 @dataclass

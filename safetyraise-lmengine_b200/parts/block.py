@@ -73,3 +73,83 @@ class PreNormBlock(Block):
         mixed = self.mixer.forward(ctx, n, run_step)
         self.ff_norm.apply(residual, mixed, n)
         return self.feed_forward.forward(ctx, n)
+
+
+@register_block("sandwich_gated")
+class SandwichGatedBlock(Block):
+    """Norms on both sides of each sublayer, and a learned gate on the sublayer's result:
+
+        n = norm_a(x);   x <- x + norm_b(sigmoid(R n + r) * sublayer(n))
+
+    once for the mixer and, if the layer has one, once for the feed-forward.  R [hidden, hidden] and r
+    read the same normed input as the sublayer.  The gate, the second norm, the addition into the float32
+    residual stream and the norm ahead of the next sublayer are one kernel (ops.gated_postnorm_add)."""
+
+    def __init__(self, spec: LayerSpec, tensors: dict, mctx):
+        from .linear import Linear
+        p = spec.weight_prefix
+        self.spec = spec
+        norm = lambda ns, name: lookup(NORMS, ns.kind, "norm")(ns, p + name, tensors, mctx)
+        self.mixer_norm = norm(spec.mixer_norm, spec.mixer_norm_name)
+        self.mixer_post_norm = norm(spec.mixer_post_norm, spec.mixer_post_norm_name)
+        self.mixer = lookup(MIXERS, spec.mixer.kind, "mixer")(spec.mixer, p, tensors, mctx)
+        self.mixer_gate = Linear(tensors[p + spec.mixer_gate_name], p + spec.mixer_gate_name)
+        self.mixer_gate_bias = tensors[p + spec.mixer_gate_name + ".b"]
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.ff_norm = norm(spec.feed_forward_norm, spec.feed_forward_norm_name)
+            self.ff_post_norm = norm(spec.feed_forward_post_norm, spec.feed_forward_post_norm_name)
+            self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
+                spec.feed_forward, p, tensors, mctx)
+            self.ff_gate = Linear(tensors[p + spec.feed_forward_gate_name], p + spec.feed_forward_gate_name)
+            self.ff_gate_bias = tensors[p + spec.feed_forward_gate_name + ".b"]
+        self.hidden = spec.mixer_norm.size
+        self.replayable = all(getattr(part, "replayable", True) for part in (self.mixer, self.feed_forward))
+
+    @classmethod
+    def tensor_decls(cls, spec: LayerSpec, prefix: str = "") -> List[TensorDecl]:
+        from ..weights.loader import MATRIX, VECTOR
+        p, H = spec.weight_prefix, spec.mixer_norm.size
+        norm = lambda ns, name: lookup(NORMS, ns.kind, "norm").tensor_decls(ns, p + name)
+        gate = lambda name: [TensorDecl(p + name, (H, H), MATRIX), TensorDecl(p + name + ".b", (H,), VECTOR)]
+        decls = (norm(spec.mixer_norm, spec.mixer_norm_name) + norm(spec.mixer_post_norm, spec.mixer_post_norm_name)
+                 + lookup(MIXERS, spec.mixer.kind, "mixer").tensor_decls(spec.mixer, p) + gate(spec.mixer_gate_name))
+        if spec.feed_forward is not None:
+            decls += (norm(spec.feed_forward_norm, spec.feed_forward_norm_name)
+                      + norm(spec.feed_forward_post_norm, spec.feed_forward_post_norm_name)
+                      + lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward").tensor_decls(spec.feed_forward, p)
+                      + gate(spec.feed_forward_gate_name))
+        return decls
+
+    def _join(self, ctx, residual, sub, gate_logits, gate_bias, post_norm, next_norm, n):
+        """residual += post_norm(sigmoid(gate) * sub); n = next_norm(residual) when something follows."""
+        from ..kernels import ops
+        ops.gated_postnorm_add(residual, sub, gate_logits, gate_bias, post_norm.weight, post_norm.spec.eps,
+                               next_norm.weight if next_norm is not None else None,
+                               next_norm.spec.eps if next_norm is not None else 0.0,
+                               n if next_norm is not None else None)
+
+    def forward(self, ctx, residual, pending, run_step: RunStep, next_block=None):
+        """See parts.base.Block.  A block of this kind behind this one gets its input already normed: the
+        kernel that adds the last sublayer's result to the residual stream applies that block's first
+        norm as well, and the NormedInput it is handed (without partial sums) says so."""
+        T = residual.shape[0]
+        n = ctx.workspace.get("block.normed", T, self.hidden, ctx.dtype)
+        if isinstance(pending, NormedInput):
+            assert pending.ss_parts is None and pending.xw.data_ptr() == n.data_ptr(), \
+                "only a block of this kind hands this block a prepared input"
+        else:
+            self.mixer_norm.apply(residual, pending, n)
+        after = next_block.mixer_norm if isinstance(next_block, SandwichGatedBlock) else None
+        handed = NormedInput(n, None, self.hidden, after.spec.eps) if after is not None else None
+
+        mixed = self.mixer.forward(ctx, n, run_step)
+        gate = self.mixer_gate(ctx, n, "block.gate")
+        self._join(ctx, residual, mixed, gate, self.mixer_gate_bias, self.mixer_post_norm,
+                   self.ff_norm if self.feed_forward is not None else after, n)
+        if self.feed_forward is None:
+            return handed
+        h = self.feed_forward.forward(ctx, n)
+        gate = self.ff_gate(ctx, n, "block.gate")
+        self._join(ctx, residual, h, gate, self.ff_gate_bias, self.ff_post_norm, after, n)
+        return handed

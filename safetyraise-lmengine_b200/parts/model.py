@@ -59,7 +59,8 @@ def cache_groups_of(spec: ModelSpec) -> List[CacheGroupSpec]:
     for i, (need, entries) in enumerate(by_need.items()):
         groups.append(CacheGroupSpec(name=f"g{i}:{need.kind}", kind=need.kind, entries=tuple(entries),
                                      kv_heads=need.kv_heads, head_dim=need.head_dim, window=need.window,
-                                     state_shape=need.state_shape, state_dtype=need.state_dtype))
+                                     state_shape=need.state_shape, state_dtype=need.state_dtype,
+                                     v_head_dim=need.v_head_dim))
     return groups
 
 

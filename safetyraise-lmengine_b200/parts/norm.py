@@ -31,3 +31,18 @@ class RMSNorm(Part):
         """residual[float32] += delta (kept when rows is None); out = norm of the sum.
         With ``rows`` only those rows are normed, into out[0..len(rows))."""
         ops.add_rmsnorm(residual, delta, self.weight, self.spec.eps, out, rows, self.spec.unit_offset)
+
+
+@register_norm("rmsnorm_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """RMSNorm whose scale is one number for all coordinates, stored as a tensor of shape ().  The number
+    is repeated over the width once, when the part is built, and the kernels of the vector norm serve."""
+    fusable = False        # the products' norm prologues and epilogues are not offered to blocks that use this norm
+
+    def __init__(self, spec: NormSpec, name: str, tensors: dict, mctx):
+        self.spec = spec
+        self.weight = tensors[name].reshape(1).expand(spec.size).contiguous()
+
+    @classmethod
+    def tensor_decls(cls, spec: NormSpec, name: str) -> List[TensorDecl]:
+        return [TensorDecl(name, (), VECTOR)]

@@ -31,3 +31,19 @@ class RotaryHalf(Part):
             ops.rope_table(ctx.positions, cos, sin, self.spec.theta, self.spec.rotary_dim)
             got = ctx.tables[self.key] = Rotation(cos, sin, self.half, interleaved=False)
         return got
+
+
+@register_position_encoding("rotary_interleaved")
+class RotaryInterleaved(RotaryHalf):
+    """The same angles, position * theta^(-2i/rotary_dim), applied to the element pairs (2i, 2i + 1)."""
+
+    def __init__(self, spec: PositionSpec, mctx):
+        super().__init__(spec, mctx)
+        self.key = ("rotary_interleaved", spec.theta, spec.rotary_dim)
+
+    def rotation(self, ctx) -> Rotation:
+        got = ctx.tables.get(self.key)
+        if got is None:
+            base = super().rotation(ctx)          # the tables do not depend on which elements form a pair
+            got = ctx.tables[self.key] = Rotation(base.cos, base.sin, base.pairs, interleaved=True)
+        return got

@@ -76,8 +76,8 @@ class SafetensorsFile:
                 raise WeightError(f"{path}: malformed entry for tensor {name!r}") from None
             if dtype not in _DTYPES:
                 raise WeightError(f"{path}: tensor {name!r} has unsupported dtype {dtype!r}")
-            if len(shape) == 0 or any((not isinstance(d, int)) or d <= 0 for d in shape):
-                raise WeightError(f"{path}: tensor {name!r} has an empty or zero-sized shape {shape}")
+            if any((not isinstance(d, int)) or d <= 0 for d in shape):     # () is a single number
+                raise WeightError(f"{path}: tensor {name!r} has a zero-sized shape {shape}")
             if not (isinstance(lo, int) and isinstance(hi, int) and 0 <= lo <= hi <= data_len):
                 raise WeightError(f"{path}: tensor {name!r} has data offsets out of range")
             count = 1
@@ -168,8 +168,9 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata=None
         t = t.detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise WeightError(f"cannot store tensor {name!r} of dtype {t.dtype}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bfloat16 \
-            else t.view(torch.int16).numpy().tobytes()
+        flat = t.reshape(-1)                          # a single number has no last dimension to view
+        raw = flat.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bfloat16 \
+            else flat.view(torch.int16).numpy().tobytes()
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)

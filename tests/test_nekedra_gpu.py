@@ -1,0 +1,365 @@
+"""Nekedra in the engine against the plain implementation (tests/plain_nekedra.py): every mixer alone and
+stacked, under every way of cutting the work, with pages and slots used again, and through the
+generation loop.  The configurations are made here; weights are random, then sharpened so that a far
+key, a sink or a mixed value shows in the logits."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+from helpers import TOL, cut_bulk_tail, cut_portions, cut_whole, note_error, random_tokens, replay
+
+import plain_nekedra as P
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+
+
+def latent(heads=3, dim=8, rot_dim=8, dims=4, rank=24, vdim=16, base=10000.0, ff=96):
+    return {"type": "latent_attention",
+            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "rot": {"base": base, "dims": dims},
+                      "kv_rank": rank, "vdim": vdim, "scale": (dim + rot_dim) ** -0.5},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def delta(heads=4, kv_heads=2, dim=16, vdim=8, conv=4, ff=96):
+    return {"type": "delta", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv},
+            "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def attention(heads=4, kv_heads=2, dim=16, vdim=24, v_mix=True, ff=96):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5}
+    if v_mix is not None:
+        m["v_mix"] = v_mix
+    return {"type": "attention", "mixer": m, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+def config(layers, width=64, vocab=200, eps=1e-6):
+    return {"architecture": "Nekedra", "layers": layers, "norm": {"eps": eps}, "vocab": vocab, "width": width}
+
+
+CONFIGS = {
+    # every mixer alone
+    "latent": config([latent()]),
+    "delta": config([delta()]),
+    "attention": config([attention(v_mix=None)]),
+    # stacked: values kept by the first attention layer and mixed by the later ones, a layer without a
+    # feed-forward, a rotation over the whole rotated part, equal key and value sizes in one layer
+    "stack": config([attention(), delta(), latent(dims=8), attention(), attention(v_mix=False, dim=16, vdim=16),
+                     delta(heads=2, kv_heads=2, dim=8, vdim=40, conv=2, ff=0), attention()]),
+    # sizes that are 1, odd or no multiple of 8: a width that the tensor-core products do not take
+    "odd": config([delta(heads=1, kv_heads=1, dim=40, vdim=33, conv=1), latent(heads=1, dim=12, rot_dim=6, dims=2, rank=20, vdim=9),
+                   attention(heads=3, kv_heads=1, dim=24, vdim=8), attention(heads=2, kv_heads=2, dim=8, vdim=8)],
+                  width=36, vocab=131, eps=1e-5),
+}
+
+
+def sharpen(tensors, cfg, seed):
+    """Random weights hide faults: with N(0, 0.02) matrices every attention is nearly uniform and a sink,
+    a far key or a decayed state changes nothing visible.  Queries and keys are scaled up so that the
+    scores spread over several units, sinks are set among the scores, decays are moved away from 1,
+    mixing weights away from 0 and 1."""
+    g = torch.Generator().manual_seed(seed)
+    rnd = lambda *shape: torch.randn(*shape, generator=g)
+    for i, layer in enumerate(cfg["layers"]):
+        p = f"l{i}.mix."
+        if layer["type"] == "attention":
+            for n in ("q", "k"):
+                tensors[p + n] = (tensors[p + n].float() * 12).to(torch.bfloat16)
+                tensors[p + n + ".b"] = 0.5 * rnd(tensors[p + n + ".b"].shape[0])
+            tensors[p + "v.b"] = 0.3 * rnd(tensors[p + "v.b"].shape[0])
+            tensors[p + "sink"] = 1.0 + rnd(tensors[p + "sink"].shape[0])
+            if p + "vmix" in tensors:
+                tensors[p + "vmix"] = torch.tensor(0.35 + 0.1 * i)
+        elif layer["type"] == "latent_attention":
+            for n in ("q", "uk"):
+                tensors[p + n] = (tensors[p + n].float() * 8).to(torch.bfloat16)
+            tensors[p + "dkv"] = (tensors[p + "dkv"].float() * 8).to(torch.bfloat16)
+        elif layer["type"] == "delta":
+            h = tensors[p + "A_log"].shape[0]
+            tensors[p + "A_log"] = -1.0 + 0.5 * rnd(h)
+            tensors[p + "dt_bias"] = 0.5 * rnd(h)
+            for n in ("a", "b", "q", "k", "v"):
+                tensors[p + n] = (tensors[p + n].float() * 20).to(torch.bfloat16)
+            for n in ("q", "k", "v"):
+                tensors[p + n + ".conv"] = (0.5 * rnd(*tensors[p + n + ".conv"].shape)).to(torch.bfloat16)
+        for n in ("rg1.b", "rg2.b"):
+            if f"l{i}.{n}" in tensors:
+                tensors[f"l{i}.{n}"] = 0.5 * rnd(tensors[f"l{i}.{n}"].shape[0])
+        for n in ("rg1", "rg2"):
+            if f"l{i}.{n}" in tensors:
+                tensors[f"l{i}.{n}"] = (tensors[f"l{i}.{n}"].float() * 10).to(torch.bfloat16)
+    return tensors
+
+
+_folders = {}
+
+
+def folder_of(name, tmp_path_factory):
+    """(folder, config, weights) of a configuration, written once per session."""
+    if name not in _folders:
+        from safetyraise_lmengine_b200.weights.random_init import write_model_folder
+        from safetyraise_lmengine_b200.weights.safetensors_io import WeightFolder, write_safetensors
+        cfg = CONFIGS[name]
+        out = write_model_folder(cfg, 40 + len(_folders), str(tmp_path_factory.mktemp("nekedra_" + name)))
+        src = WeightFolder(out)
+        tensors = sharpen({n: src.get(n).clone() for n in src.names()}, cfg, 7 + len(_folders))
+        del src
+        write_safetensors(os.path.join(out, "model.safetensors"), tensors)
+        _folders[name] = (out, cfg, tensors)
+    return _folders[name]
+
+
+@pytest.fixture(scope="session", params=list(CONFIGS))
+def model(request, tmp_path_factory):
+    return (request.param,) + folder_of(request.param, tmp_path_factory)
+
+
+_plain = {}
+
+
+def plain(name, cfg, W, tokens):
+    key = (name, tuple(tokens))
+    if key not in _plain:
+        _plain[key] = P.forward(cfg, W, tokens).numpy()
+    return _plain[key]
+
+
+def build(folder, dtype, num_pages=64, page_size=16, **kw):
+    from safetyraise_lmengine_b200 import Engine
+    kw.setdefault("max_context", 1024)
+    return Engine.from_folder(folder, dtype=dtype, page_size=page_size, num_pages=num_pages, max_requests=4,
+                              max_batch_tokens=512, **kw)
+
+
+def check(got, model, requests, dtype):
+    name, _, cfg, W = model
+    for rid, tokens in requests.items():
+        ref = plain(name, cfg, W, tokens)
+        rows = np.stack([got[(rid, p)] for p in range(len(tokens))])
+        err = np.abs(rows.astype(np.float64) - ref).max(axis=1) / np.abs(ref).max()
+        bad = np.nonzero(err > TOL[dtype])[0]
+        assert bad.size == 0, (f"{name} request {rid}: first wrong position {bad[0]} of {len(tokens)} "
+                               f"(rel err {err[bad[0]]:.3e} > {TOL[dtype]:.0e}); wrong positions {bad[:20]}")
+        note_error(dtype, float(err.max()), "nekedra " + name)
+
+
+def requests_for(cfg, lens=(1, 7, 33, 64, 100), seed=0):
+    rng = np.random.default_rng(300 + seed)
+    return {f"r{i}": random_tokens(rng, n, cfg["vocab"]) for i, n in enumerate(lens)}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_whole_requests_alone(model, dtype):
+    eng = build(model[1], dtype)
+    reqs = requests_for(model[2])
+    got = {}
+    for rid, toks in reqs.items():
+        got.update(replay(eng, cut_whole(rid, toks)))
+    check(got, model, reqs, dtype)
+    assert eng.cache.audit() == 0 and eng.cache.free_pages() == 64
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prefill_then_token_by_token(model, dtype):
+    """Most of a prompt in one step, the rest decoded one by one (replayed from CUDA graphs)."""
+    eng = build(model[1], dtype)
+    reqs = {k: v for k, v in requests_for(model[2]).items() if len(v) >= 33}
+    got = {}
+    for rid, toks in reqs.items():
+        got.update(replay(eng, cut_bulk_tail(rid, toks, 32)))
+    check(got, model, reqs, dtype)
+    if getattr(eng.model, "replayable", True):
+        assert eng.graph_replays > 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_token_at_a_time_from_the_start(model, dtype):
+    eng = build(model[1], dtype)
+    reqs = requests_for(model[2], lens=(45,), seed=2)
+    got = replay(eng, cut_bulk_tail("r0", reqs["r0"], 44))
+    check(got, model, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("page_size", [4, 16])
+def test_portions_of_changing_size(model, dtype, page_size):
+    """Portions down to two tokens, cut in the middle of pages, of key blocks and of the convolution's reach."""
+    eng = build(model[1], dtype, num_pages=40, page_size=page_size)
+    reqs = {k: v for k, v in requests_for(model[2]).items() if len(v) >= 2}
+    got = {}
+    for rid, toks in reqs.items():
+        got.update(replay(eng, cut_portions(rid, toks)))
+        got.update({(rid + "b", p): row for (_, p), row in
+                    replay(eng, cut_portions(rid, toks, sizes=(2, 2, 3, 2, 29, 2, 2, 35, 2))).items()})
+    check(got, model, reqs, dtype)
+    check(got, model, {rid + "b": toks for rid, toks in reqs.items()}, dtype)
+    assert eng.cache.audit() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_requests_in_one_batch_and_reuse_of_pages_and_slots(model, dtype):
+    """Up to four live requests: portions of some beside single tokens of others; requests end and new
+    ones take their slots and pages (few pages, so the page freed last is used next)."""
+    cfg = model[2]
+    rng = np.random.default_rng(9)
+    lens = {"a": 70, "b": 23, "c": 41, "d": 9, "e": 55, "f": 30, "g": 12}
+    reqs = {k: random_tokens(rng, n, cfg["vocab"]) for k, n in lens.items()}
+    fed = {k: 0 for k in reqs}
+
+    def take(rid, n):
+        lo = fed[rid]
+        hi = min(len(reqs[rid]), lo + n)
+        fed[rid] = hi
+        return (rid, reqs[rid][lo:hi], list(range(hi - lo)))
+
+    steps = [
+        {"entries": [take("a", 20), take("b", 5)]},
+        {"entries": [take("a", 1), take("b", 18), take("c", 2), take("d", 8)], "end": ["b"]},
+        {"entries": [take("a", 1), take("c", 30), take("d", 1), take("e", 7)], "end": ["d"]},
+        {"entries": [take("f", 30), take("a", 48), take("c", 1), take("e", 2)], "end": ["a", "f"]},
+        {"entries": [take("g", 3), take("c", 8), take("e", 1)], "end": ["c"]},
+        {"entries": [take("e", 45), take("g", 1)]},
+        {"entries": [take("g", 8)], "end": ["e", "g"]},
+    ]
+    assert all(fed[k] == len(reqs[k]) for k in reqs)
+    eng = build(model[1], dtype, num_pages=24, page_size=8)
+    got = replay(eng, steps)
+    check(got, model, reqs, dtype)
+    opened, reused = eng.cache.reuse_counts()
+    assert reused > 0 and eng.cache.audit() == 0 and eng.cache.free_pages() == 24
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model, dtype):
+    """300 tokens, the last 260 one by one: pages fill and turn over, the recurrent state is carried far."""
+    reqs = requests_for(model[2], lens=(300,), seed=3)
+    eng = build(model[1], dtype, num_pages=24, page_size=16)
+    got = replay(eng, cut_bulk_tail("r0", reqs["r0"], 260))
+    check(got, model, reqs, dtype)
+
+
+def test_cuttings_agree_bit_for_bit_in_float32(model):
+    """In float32 no sum depends on the cutting: the logits of a position are the same bits."""
+    reqs = requests_for(model[2], lens=(90,), seed=4)
+    toks = reqs["r0"]
+    eng = build(model[1], "float32")
+    whole = replay(eng, cut_whole("r0", toks))
+    tail = replay(eng, cut_bulk_tail("r0", toks, 40))
+    parts = replay(eng, cut_portions("r0", toks))
+    for p in range(len(toks)):
+        assert np.array_equal(whole[("r0", p)], tail[("r0", p)]), p
+        assert np.array_equal(whole[("r0", p)], parts[("r0", p)]), p
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_failed_step_puts_the_state_back(model, dtype):
+    """A step refused for a token outside the vocabulary leaves nothing behind; the request then goes on
+    as if the step had never been tried (the recurrent state and the convolution's inputs included)."""
+    from safetyraise_lmengine_b200 import StepEntry
+    from safetyraise_lmengine_b200.errors import ShapeError
+    reqs = requests_for(model[2], lens=(30,), seed=5)
+    toks = reqs["r0"]
+    eng = build(model[1], dtype)
+    slot = eng.open_request()
+    rows = [eng.step([StepEntry(slot, toks[:11], list(range(11)))]).cpu().numpy().copy()]
+    with pytest.raises(ShapeError):
+        eng.step([StepEntry(slot, [model[2]["vocab"] + 5, 1], [0])])
+    rows.append(eng.step([StepEntry(slot, toks[11:], list(range(19)))]).cpu().numpy().copy())
+    check({("r0", p): r for p, r in enumerate(np.concatenate(rows))}, model, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_scheduler(model, dtype):
+    from safetyraise_lmengine_b200 import LLM, SamplingParams
+    name, folder, cfg, W = model
+    rng = np.random.default_rng(21)
+    prompts = [random_tokens(rng, n, cfg["vocab"]) for n in (5, 19, 11, 3, 26)]        # more requests than slots
+    llm = LLM.from_folder(folder, dtype=dtype, page_size=4, num_pages=64, max_active=3, max_batch_tokens=48,
+                          prefill_chunk=8, max_context=128, queue_capacity=8)
+    llm.eos = set()
+    res = llm.generate(prompts, SamplingParams(temperature=0.0, max_new_tokens=10))
+    for prompt, r in zip(prompts, res):
+        assert r.finish_reason == "length" and len(r.tokens) == 10
+        toks = list(prompt) + list(r.tokens)
+        ref = P.forward(cfg, W, toks[:-1]).numpy()
+        for i, tok in enumerate(r.tokens):
+            row = ref[len(prompt) - 1 + i]
+            if dtype == "float32":
+                assert tok == int(np.argmax(row)) or row[tok] >= row.max() - 1e-5 * np.abs(row).max(), (i, tok)
+            else:
+                assert row[tok] >= row.max() - 2 * TOL[dtype] * np.abs(row).max(), (i, tok)
+    assert llm.engine.cache.audit() == 0 and llm.engine.cache.free_pages() == 64
+
+
+# ---- mechanisms alone, with inputs made so that a fault shows --------------------------------------------------
+
+class _Ctx:
+    """The fields of a step's context that the attention kernel's wrapper reads."""
+    def __init__(self, q_lens, kv_lens, dev):
+        self.n_entries, self.max_q_len = len(q_lens), max(q_lens)
+        self.cu_q = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=dev)
+        self.kv_lens = torch.tensor(kv_lens, dtype=torch.int32, device=dev)
+
+
+def _paged(keys, page_size, order, dtype, dev):
+    """keys [L, heads, d] -> (pool [pages, heads, page_size, d], table) with the pages in the given order."""
+    L, H, d = keys.shape
+    n = (L + page_size - 1) // page_size
+    pool = torch.zeros(len(order), H, page_size, d, dtype=dtype, device=dev)
+    for i in range(n):
+        chunk = keys[i * page_size:(i + 1) * page_size]
+        pool[order[i], :, :chunk.shape[0]] = chunk.transpose(0, 1).to(dtype)
+    return pool, torch.tensor([order[:n]], dtype=torch.int32, device=dev)
+
+
+@pytest.mark.parametrize("cache_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dk,dv,heads,kv_heads,from_keys", [(24, 40, 4, 2, False), (48, 16, 3, 3, False),
+                                                           (72, 64, 5, 1, True), (16, 16, 2, 1, False)])
+def test_attention_kernel_far_keys_page_borders_and_sinks(cache_dtype, dk, dv, heads, kv_heads, from_keys):
+    """One key far back (and one right at a page border, one at the first position) carries most of a
+    row's weight: losing it, or a sink, changes the result by far more than the tolerance."""
+    from safetyraise_lmengine_b200.kernels import ops
+    dev, L, page = "cuda:0", 700, 16
+    g = torch.Generator().manual_seed(dk * 100 + dv)
+    q = torch.randn(L, heads, dk, generator=g)
+    k = torch.randn(L, kv_heads, dk, generator=g)
+    v = k[..., :dv].clone() if from_keys else torch.randn(L, kv_heads, dv, generator=g)
+    if cache_dtype == torch.bfloat16:
+        k, v = k.bfloat16().float(), v.bfloat16().float()
+    rep = heads // kv_heads
+    for row, col in ((L - 1, 3), (L - 2, 0), (600, 15), (601, 16), (650, 319), (651, 320), (40, 40)):
+        q[row] = 6.0 * k[col].repeat_interleave(rep, 0) / k[col].norm(dim=-1, keepdim=True).repeat_interleave(rep, 0)
+    sink = torch.tensor([0.5, 3.0, -1.0, 6.0, 2.0][:heads])
+    scale = 0.9
+    scores = torch.einsum("ihd,jhd->hij", q.double(), k.double().repeat_interleave(rep, 1)) * scale
+    ref = torch.einsum("hij,jhd->ihd", P.causal_softmax(scores, sink.double()), v.double().repeat_interleave(rep, 1))
+    no_sink = torch.einsum("hij,jhd->ihd", P.causal_softmax(scores), v.double().repeat_interleave(rep, 1))
+    assert (ref - no_sink).abs().max() > 0.05                    # the sink matters in this test
+    order = list(reversed(range(L // page + 2)))                 # pages in an order that is not the sequence's
+    k_pool, table = _paged(k, page, order, cache_dtype, dev)
+    v_pool = None if from_keys else _paged(v, page, order, cache_dtype, dev)[0]
+    tol = 2e-5 if cache_dtype == torch.float32 else 2e-2
+    for q_lens in ([L], [1], [2], [33]):                         # a whole prompt, one decoded token, short portions
+        n = q_lens[0]
+        out = torch.zeros(n, heads * dv, dtype=torch.float32, device=dev)
+        ops.paged_attention_general(_Ctx(q_lens, [L], dev), q[L - n:].reshape(n, -1).contiguous().to(dev), k_pool, v_pool,
+                                    out, table, sink.to(dev), heads, kv_heads, dk, dv, scale)
+        err = (out.cpu().double().view(n, heads, dv) - ref[L - n:]).abs().max() / ref.abs().max()
+        assert err < tol, (q_lens, float(err))
+
+
+def test_postnorm_kernel_against_the_formula():
+    from safetyraise_lmengine_b200.kernels import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(3)
+    for T, H in ((5, 36), (3, 1000), (2, 5000)):
+        res, sub, gate = torch.randn(T, H, generator=g), 3 * torch.randn(T, H, generator=g), torch.randn(T, H, generator=g)
+        bias, pw, nw = torch.randn(H, generator=g), torch.full((H,), 1.3), torch.full((H,), 0.7)
+        y = sub.double() * torch.sigmoid(gate.double() + bias.double())
+        want = res.double() + P.scalar_rms_norm(y, 1.3, 1e-6)
+        want_next = P.scalar_rms_norm(want, 0.7, 1e-5)
+        r, n = res.to(dev), torch.zeros(T, H, device=dev)
+        ops.gated_postnorm_add(r, sub.to(dev), gate.to(dev), bias.to(dev), pw.to(dev), 1e-6, nw.to(dev), 1e-5, n)
+        assert (r.cpu().double() - want).abs().max() < 1e-5 and (n.cpu().double() - want_next).abs().max() < 1e-5

@@ -103,7 +103,7 @@ def _write_raw(path, header: dict, data: bytes, dup=None):
 
 @pytest.mark.parametrize("header, data, dup", [
     ({"a": {"dtype": "F64", "shape": [1], "data_offsets": [0, 8]}}, b"\0" * 8, None),
-    ({"a": {"dtype": "F32", "shape": [], "data_offsets": [0, 4]}}, b"\0" * 4, None),
+    ({"a": {"dtype": "F32", "shape": [], "data_offsets": [0, 8]}}, b"\0" * 8, None),        # one number, 8 bytes
     ({"a": {"dtype": "F32", "shape": [0], "data_offsets": [0, 0]}}, b"", None),
     ({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 4]}}, b"\0" * 8, None),       # byte length
     ({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]}}, b"\0" * 4, None),       # out of range
@@ -188,3 +188,13 @@ def test_stored_types_of_random_folders(tmp_path):
     assert m.dtype == torch.float32 and not torch.equal(m, m.to(torch.bfloat16).float())
     with pytest.raises(ValueError):
         write_model_folder(TINY_A, 9, str(tmp_path / "x"), store="F8")
+
+
+def test_a_single_number_is_a_tensor(tmp_path):
+    """A tensor of shape () holds one number: written, read back and checked like any other."""
+    from safetyraise_lmengine_b200.weights.safetensors_io import write_safetensors
+    p = str(tmp_path / "one.safetensors")
+    write_safetensors(p, {"g": torch.tensor(1.25, dtype=torch.bfloat16), "w": torch.ones(2, 3)})
+    f = SafetensorsFile(p)
+    assert f.meta("g")[1] == () and f.get("g").shape == () and float(f.get("g")) == 1.25
+    assert f.get("w").shape == (2, 3)
