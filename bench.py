@@ -134,7 +134,7 @@ def build_engine(config: dict, layers: int, max_requests: int, tokens_in_cache: 
     from safetyraise_lmengine_b200 import Engine, spec_from_config
     from safetyraise_lmengine_b200.parts.model import tensor_decls
     from safetyraise_lmengine_b200.weights.random_init import RandomWeights
-    cfg = dict(config, num_hidden_layers=layers)
+    cfg = dict(config, num_hidden_layers=layers) if "num_hidden_layers" in config else dict(config)
     spec = spec_from_config(cfg)
     src = RandomWeights(tensor_decls(spec), seed=0, device="cuda:0")
     num_pages = (tokens_in_cache + PAGE_SIZE - 1) // PAGE_SIZE + max_requests
@@ -148,7 +148,8 @@ def build_engine(config: dict, layers: int, max_requests: int, tokens_in_cache: 
 def randomize_cache(eng):
     """Random cache contents, N(0, 1).  The work does not depend on the values, the power does: at its power cap
     the GPU runs a 32B decode step of batch 64 in 23.4 ms over such contents and in 22.2 ms over zeros."""
-    for pool in eng.cache.kv_pools.values():
+    pools = list(eng.cache.kv_pools.values()) + list(eng.cache.k_pools.values()) + list(eng.cache.v_pools.values())
+    for pool in pools:
         flat = pool.view(-1)
         step = 1 << 26
         for lo in range(0, flat.numel(), step):
@@ -528,6 +529,69 @@ def run_mixed(args, shape: str, pk) -> dict:
     }
 
 
+# ---- Nekedra beside the Qwen3 decoder at equal layer sizes (--design nekedra) ---------------------------------
+DESIGN_SIZES = {"2048": dict(width=2048, heads=16, kv_heads=4), "4096": dict(width=4096, heads=32, kv_heads=8)}
+DESIGN_VOCAB = 32768
+DESIGN_LAYERS = 4
+
+
+def nekedra_config(size: dict, kinds) -> dict:
+    """A Nekedra configuration whose layers have the sizes of a Qwen3 layer of the same width: heads of 128,
+    a feed-forward of three widths; the latent of 512 with a rotated part of 64 per head."""
+    W, H, G = size["width"], size["heads"], size["kv_heads"]
+    mixers = {
+        "attention": {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "v_mix": True},
+        "latent_attention": {"heads": H, "dim": 128, "rot_dim": 64, "rot": {"base": 1e6, "dims": 64}, "kv_rank": 512,
+                             "vdim": 128, "scale": 192 ** -0.5},
+        "delta": {"heads": H, "kv_heads": H // 2, "dim": 128, "vdim": 128, "conv": 4},
+    }
+    return {"architecture": "Nekedra", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6},
+            "layers": [{"type": k, "mixer": mixers[k], "mlp": {"kind": "dense", "ff": 3 * W}} for k in kinds]}
+
+
+def qwen3_config(size: dict) -> dict:
+    return dict(BASE, num_hidden_layers=DESIGN_LAYERS, hidden_size=size["width"], num_attention_heads=size["heads"],
+                num_key_value_heads=size["kv_heads"], intermediate_size=3 * size["width"], vocab_size=DESIGN_VOCAB)
+
+
+def run_design(args) -> dict:
+    """Prefill (2,048 tokens, one request) and decode (batch 8 behind 2,048 tokens) of four-layer models with
+    random weights: the Qwen3 decoder, and Nekedra stacks of each mixer alone and of all three, at equal
+    widths, heads and feed-forward sizes.  Times of whole steps through the step function, CUDA events,
+    three warm-ups; beside each the kernels that take the most time of an eager step."""
+    import torch
+    batch, context = 8, CONTEXT["8b"]
+    stacks = {"qwen3": None, "nekedra attention": ["attention"] * DESIGN_LAYERS,
+              "nekedra latent": ["latent_attention"] * DESIGN_LAYERS, "nekedra delta": ["delta"] * DESIGN_LAYERS,
+              "nekedra mixed": ["latent_attention", "delta", "attention", "delta"]}
+    out = {"metric": "nekedra_beside_qwen3", "layers": DESIGN_LAYERS, "prefill_tokens": PREFILL_TOKENS,
+           "decode_batch": batch, "decode_context": context, "dtype": "bf16", "data": "synthetic", "sizes": {}}
+    sizes = [args.design_size] if args.design_size else sorted(DESIGN_SIZES)
+    for name in sizes:
+        size, rows = DESIGN_SIZES[name], {}
+        for label, kinds in stacks.items():
+            cfg = qwen3_config(size) if kinds is None else nekedra_config(size, kinds)
+            eng = build_engine(cfg, DESIGN_LAYERS, batch + 1, batch * (context + MAX_GROWTH) + PREFILL_TOKENS,
+                               PREFILL_TOKENS)
+            randomize_cache(eng)
+            prefill_ms = time_prefill(eng, PREFILL_TOKENS, 3)
+            ptable = prefill_kernel_table(eng, PREFILL_TOKENS, top=6)
+            slots = fill_contexts(eng, batch, context)
+            d = time_decode(eng, slots, context, args.steps, args.warmup, 0.5)
+            dtable = kernel_table(eng, slots, context, top=6)
+            rows[label] = {"prefill_ms": round(prefill_ms, 3),
+                           "prefill_tok_s": round(PREFILL_TOKENS / prefill_ms * 1000.0, 1),
+                           "decode_ms_per_step": round(d["ms_per_step"], 4),
+                           "decode_tok_s": round(batch / d["ms_per_step"] * 1000.0, 1),
+                           "decode_launches_per_step": d["launches"] // max(args.steps, 1),
+                           "weight_bytes": eng.model.weight_bytes(),
+                           "prefill_kernels": ptable, "decode_kernels": dtable}
+            del eng, slots
+            torch.cuda.empty_cache()
+        out["sizes"][name] = rows
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -545,6 +609,10 @@ def main() -> int:
     ap.add_argument("--only-prefill", action="store_true", help="run just the 2,048-token prefill (for profilers)")
     ap.add_argument("--streaming-kernel", action="store_true",
                     help="steps of up to 8 tokens on the weight-streaming mma.sync kernel instead of the tensor-core one")
+    ap.add_argument("--design", default=None, choices=["nekedra"],
+                    help="instead of the default workload: prefill and decode of Nekedra stacks beside the Qwen3 "
+                         "decoder at equal layer sizes")
+    ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="one width of --design")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
                     help="repeat the block of --steps steps until this much is timed (0: one block, for profilers)")
     args = ap.parse_args()
@@ -558,6 +626,11 @@ def main() -> int:
     if args.streaming_kernel:
         from safetyraise_lmengine_b200.kernels import ops
         ops.skinny_max_tokens = 8
+    if args.design:
+        if args.steps == 100:
+            args.steps = 20
+        print(json.dumps(run_design(args)))
+        return 0
     pk = peaks()
     out = run_mixed(args, args.shape, pk) if workload == "mixed" else run_decode(args, args.shape, pk)
     print(json.dumps(out))

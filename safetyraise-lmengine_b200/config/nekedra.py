@@ -88,13 +88,18 @@ def read_spec(root: dict) -> ModelSpec:
     if not isinstance(entries, list) or not entries or len(entries) > MAX_LAYERS:
         raise ConfigError(f"config.json: 'layers' must list 1 to {MAX_LAYERS} layers")
     norm = NormSpec("rmsnorm_scalar", width, eps)
-    layers, keeps_values = [], False
+    layers, keeps_values, kept_size = [], False, 0
     for i, entry in enumerate(entries):
         where = f"layers[{i}]."
         if not isinstance(entry, dict) or not isinstance(entry.get("type"), str):
             raise ConfigError(f"config.json: {where[:-1]} must be an object with a 'type'")
         mixer = _mixer(entry["type"], _obj(entry, "mixer", where), width, eps, where + "mixer.", keeps_values)
-        keeps_values = keeps_values or getattr(mixer, "value_mix", "") == "keep"
+        if getattr(mixer, "value_mix", ""):
+            size = mixer.kv_heads * mixer.v_head_dim
+            if keeps_values and size != kept_size:
+                raise ConfigError(f"config.json: {where}mixer mixes values of {size} elements per token with the "
+                                  f"{kept_size} that the first such layer keeps")
+            keeps_values, kept_size = True, size
         ff = None
         if entry.get("mlp") is not None:
             mlp = _obj(entry, "mlp", where)

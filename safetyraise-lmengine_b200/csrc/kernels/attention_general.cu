@@ -28,13 +28,17 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
                                const TC* __restrict__ v_cache, TO* __restrict__ out,
                                const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
                                const int* __restrict__ kv_lens, const float* __restrict__ sinks, int nq, int nkv,
-                               int dk, int dv, int page_size, float scale, int window) {
+                               int dk, int dv, int page_size, float scale, int window, int nsplit, int kv_chunk,
+                               float* __restrict__ part_o, float* __restrict__ part_ml) {
   extern __shared__ float smem[];
   const int e = blockIdx.z, kvh = blockIdx.y;
   const int G = nq / nkv;
   const int t0 = cu_q[e], q_len = cu_q[e + 1] - t0, kv_len = kv_lens[e];
   const int rows = q_len * G;
-  const int r0 = blockIdx.x * kRows;
+  // nsplit > 1 (entries of at most kRows rows): blockIdx.x is a slice of kv_chunk keys, not a row tile;
+  // the slices' unnormalised sums go to part_o / part_ml and attention_merge_kernel adds them
+  const bool sliced = nsplit > 1;
+  const int r0 = sliced ? 0 : blockIdx.x * kRows;
   if (r0 >= rows) return;
   const int ks = dk + 1;                                   // padded key row: lanes read different banks
   float* q_s = smem;                                       // [kRows][dk]
@@ -60,21 +64,27 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
     pos[i] = live ? start + row / G : -1;                  // a row beyond the entry sees no key
     first[i] = (window > 0 && live) ? max(0, pos[i] - window + 1) : 0;
     const int h = kvh * G + (live ? row % G : 0);
-    m[i] = sinks ? sinks[h] : -CUDART_INF_F;
-    l[i] = sinks ? 1.f : 0.f;
+    const bool with_sink = sinks && (!sliced || blockIdx.x == 0);     // the sink counts once
+    m[i] = with_sink ? sinks[h] : -CUDART_INF_F;
+    l[i] = with_sink ? 1.f : 0.f;
 #pragma unroll
     for (int c = 0; c < VPL; ++c) acc[i][c] = 0.f;
   }
   const int last_row = min(rows, r0 + kRows) - 1;
   const int max_pos = start + last_row / G, min_pos = start + r0 / G;
-  const int first_key = window > 0 ? max(0, min_pos - window + 1) : 0;
+  int first_key = window > 0 ? max(0, min_pos - window + 1) : 0;
+  int last_key = max_pos;
+  if (sliced) {                                            // kv_chunk is a multiple of kKeys
+    first_key = max(first_key, (int)blockIdx.x * kv_chunk);
+    last_key = min(last_key, ((int)blockIdx.x + 1) * kv_chunk - 1);
+  }
 
-  for (int jb = (first_key / kKeys) * kKeys; jb <= max_pos; jb += kKeys) {
+  for (int jb = (first_key / kKeys) * kKeys; jb <= last_key; jb += kKeys) {
     __syncthreads();                                       // the tile of the iteration before is no longer read
     for (int idx = tid; idx < kKeys * dk; idx += blockDim.x) {
       const int jj = idx / dk, d = idx - jj * dk, j = jb + jj;
       float v = 0.f;
-      if (j <= max_pos) {
+      if (j <= last_key) {
         const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
         v = to_float(k_cache[rowi * dk + d]);
       }
@@ -84,7 +94,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
       for (int idx = tid; idx < kKeys * dv; idx += blockDim.x) {
         const int jj = idx / dv, d = idx - jj * dv, j = jb + jj;
         float v = 0.f;
-        if (j <= max_pos) {
+        if (j <= last_key) {
           const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
           v = to_float(v_cache[rowi * dv + d]);
         }
@@ -121,7 +131,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
       p_s[(warp * kRowsPerWarp + i) * kKeys + lane] = p;
     }
     __syncwarp();
-    const int n_here = min(kKeys, max_pos - jb + 1);
+    const int n_here = min(kKeys, last_key - jb + 1);
     for (int jj = 0; jj < n_here; ++jj) {
       float pj[kRowsPerWarp];
 #pragma unroll
@@ -142,6 +152,19 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
   for (int i = 0; i < kRowsPerWarp; ++i) {
     const int row = r0 + warp * kRowsPerWarp + i;
     if (row >= rows) continue;
+    if (sliced) {
+      const size_t slab = (((size_t)e * nkv + kvh) * nsplit + blockIdx.x) * kRows + (row - r0);
+#pragma unroll
+      for (int c = 0; c < VPL; ++c) {
+        const int col = lane + 32 * c;
+        if (col < dv) part_o[slab * dv + col] = acc[i][c];
+      }
+      if (lane == 0) {
+        part_ml[slab * 2] = m[i];
+        part_ml[slab * 2 + 1] = l[i];
+      }
+      continue;
+    }
     const float inv = 1.f / l[i];
     TO* o = out + ((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dv;
 #pragma unroll
@@ -149,6 +172,36 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
       const int col = lane + 32 * c;
       if (col < dv) o[col] = from_float<TO>(acc[i][c] * inv);
     }
+  }
+}
+
+// One warp per (entry, KV head, row): adds the slices' sums in slice order.
+template <typename TO>
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       TO* __restrict__ out, const int* __restrict__ cu_q, int n_entries, int nq,
+                                       int nkv, int dv, int nsplit) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)n_entries * nkv * kRows) return;
+  const int r = (int)(w % kRows), kvh = (int)((w / kRows) % nkv), e = (int)(w / ((long long)kRows * nkv));
+  const int G = nq / nkv, t0 = cu_q[e], rows = (cu_q[e + 1] - t0) * G;
+  if (r >= rows) return;
+  const size_t first = (((size_t)e * nkv + kvh) * nsplit) * kRows + r;
+  float M = -CUDART_INF_F;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(first + (size_t)s * kRows) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = part_ml[(first + (size_t)s * kRows) * 2];
+    if (ms != -CUDART_INF_F) L += part_ml[(first + (size_t)s * kRows) * 2 + 1] * expf(ms - M);
+  }
+  TO* o = out + ((size_t)(t0 + r / G) * nq + kvh * G + r % G) * dv;
+  for (int col = lane; col < dv; col += 32) {
+    float a = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = part_ml[(first + (size_t)s * kRows) * 2];
+      if (ms != -CUDART_INF_F) a += part_o[(first + (size_t)s * kRows) * dv + col] * expf(ms - M);
+    }
+    o[col] = from_float<TO>(a / L);
   }
 }
 
@@ -190,14 +243,15 @@ template <typename TC, typename TO>
 static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, const float* q, const void* k_cache,
                           const void* v_cache, void* out, const int* block_table, int table_stride, const int* cu_q,
                           const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
-                          float scale, int window) {
+                          float scale, int window, int nsplit, int kv_chunk, float* part_o, float* part_ml,
+                          int n_entries) {
 #define SRLM_GENERAL_CASE(V)                                                                                   \
   case V: {                                                                                                    \
     auto kern = paged_attention_general_kernel<TC, TO, V>;                                                     \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     kern<<<grid, kWarps * 32, smem, stream>>>(q, (const TC*)k_cache, (const TC*)v_cache, (TO*)out, block_table, \
                                               table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size,  \
-                                              scale, window);                                                  \
+                                              scale, window, nsplit, kv_chunk, part_o, part_ml);               \
     break;                                                                                                     \
   }
   switch (vpl) {
@@ -208,6 +262,11 @@ static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, 
     SRLM_GENERAL_CASE(16)
   }
 #undef SRLM_GENERAL_CASE
+  if (nsplit > 1) {
+    const long long warps = (long long)n_entries * nkv * kRows;
+    attention_merge_kernel<TO><<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(part_o, part_ml, (TO*)out, cu_q,
+                                                                                n_entries, nq, nkv, dv, nsplit);
+  }
   return launched();
 }
 
@@ -221,8 +280,8 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
                                             int cache_dtype, int out_dtype, const int* block_table,
                                             int table_stride, const int* cu_q, const int* kv_lens,
                                             const float* sinks, int n_entries, int max_q_len, int nq, int nkv,
-                                            int dk, int dv, int page_size, float scale, int window,
-                                            cudaStream_t stream) {
+                                            int dk, int dv, int page_size, float scale, int window, int nsplit,
+                                            int kv_chunk, float* part_o, float* part_ml, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
   if (nq <= 0 || nkv <= 0 || nq % nkv || dk <= 0 || dv <= 0 || dv > 512 || page_size <= 0 || (!v_cache && dv > dk))
     return refuse(ST_BAD_SIZE, "paged_attention_general: nq=%d nkv=%d dk=%d dv=%d page_size=%d (dv <= 512; values "
@@ -233,18 +292,25 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
   if (smem > 220 * 1024) return refuse(ST_BAD_SIZE, "paged_attention_general: dk=%d dv=%d need %zu bytes of shared memory", dk, dv, smem);
   const int G = nq / nkv;
   const long long tiles = ((long long)max_q_len * G + kRows - 1) / kRows;
-  dim3 grid((unsigned)tiles, (unsigned)nkv, (unsigned)n_entries);
+  if (nsplit > 1 && (tiles != 1 || kv_chunk <= 0 || kv_chunk % kKeys || !part_o || !part_ml))
+    return refuse(ST_BAD_SIZE, "paged_attention_general: %d slices of %d keys need entries of at most %d rows, slices "
+                  "of whole key blocks and a workspace", nsplit, kv_chunk, kRows);
+  if (nsplit < 1) nsplit = 1;
+  dim3 grid((unsigned)(nsplit > 1 ? nsplit : tiles), (unsigned)nkv, (unsigned)n_entries);
   int vpl = 1;
   while (vpl * 32 < dv) vpl <<= 1;
   if (cache_dtype == DT_F32 && out_dtype == DT_F32)
     return launch_general<float, float>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
-                                        cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window);
+                                        cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
+                                        part_o, part_ml, n_entries);
   if (cache_dtype == DT_BF16 && out_dtype == DT_F32)
     return launch_general<bf16, float>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
-                                       cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window);
+                                       cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
+                                        part_o, part_ml, n_entries);
   if (cache_dtype == DT_BF16 && out_dtype == DT_BF16)
     return launch_general<bf16, bf16>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
-                                      cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window);
+                                      cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
+                                        part_o, part_ml, n_entries);
   return refuse(ST_BAD_DTYPE, "paged_attention_general: cache dtype %d with output dtype %d", cache_dtype, out_dtype);
 }
 

@@ -39,7 +39,7 @@ def main(argv=None) -> int:
     num_pages = (args.max_tokens + PAGE_SIZE - 1) // PAGE_SIZE
     engine = Engine.from_folder(args.model, dtype=args.dtype, page_size=PAGE_SIZE, num_pages=num_pages,
                                 max_requests=MAX_LIVE, max_batch_tokens=max(args.max_tokens, 64),
-                                max_context=None)
+                                max_context=num_pages * PAGE_SIZE)     # no request can hold more than the pool
     print("trace_run: ready", file=sys.stderr, flush=True)
 
     slots = {}

@@ -70,6 +70,8 @@ class KernelLibrary:
         self.split_mixed_min_blocks = None      # ... when they make this many blocks (None: one per SM)
         self.fuse_norms_into_products = True    # steps of up to 128 tokens: the blocks' norms inside the products
         self.early_launch = True                # weight-streaming products may start under the kernel ahead of them
+        self.split_general_attention = True     # decode steps of the general attention: the keys in slices
+        self.general_attention_on_tensor_cores = True   # its prompts and portions: mma.sync, when the sizes fit
 
     @property
     def lib(self):
@@ -752,19 +754,51 @@ class KernelLibrary:
             "gated_postnorm_add")
 
     # ---- attention with separate key and value sizes ---------------------------------------
+    GENERAL_ROWS = 16        # rows (tokens x query heads of a KV head) of a block of the general attention kernel
+
     def paged_attention_general(self, ctx, q, k_cache, v_cache, out, block_table, sinks, nq, nkv, dk, dv, scale,
                                 window=0):
         """Causal attention of the batch of ``ctx`` over pages whose keys have dk and whose values have dv
         elements (v_cache None: the values are the keys' first dv elements).  q float32 [T, nq * dk];
         k_cache [pages, nkv, page_size, dk]; out [T, nq * dv], float32 or the cache's dtype; sinks float32
-        [nq] or None: one more term exp(sink) in each head's softmax denominator."""
+        [nq] or None: one more term exp(sink) in each head's softmax denominator.
+
+        A bfloat16 cache and more than 16 rows in some entry (prompts, portions, mixed steps): the tensor-core
+        form (attention_general_mma.cu) when it takes the sizes.
+        When every entry has at most 16 rows (decode steps) and the cache is bfloat16, the keys are cut into
+        slices with a block each, as many as run at the same time, and a second kernel adds them; the
+        float32 path keeps one block per entry and KV head, whose sums do not depend on the batch."""
         if q.dtype != torch.float32:
             raise ShapeError("paged_attention_general: float32 queries")
+        n = ctx.n_entries
+        decode = ctx.max_q_len * (nq // nkv) <= self.GENERAL_ROWS
+        if (k_cache.dtype == torch.bfloat16 and not decode and self.general_attention_on_tensor_cores
+                and self.lib.srlm_attention_general_mma_takes(C.c_int(dk), C.c_int(dv), C.c_int(int(v_cache is None)))):
+            # prompts and their portions: bfloat16 tensor cores (the queries are rounded as they are loaded)
+            self._check(self.lib.srlm_paged_attention_general_mma(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), dtype_code(out.dtype), _ptr(block_table),
+                C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks), C.c_int(n),
+                C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
+                C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), _stream()),
+                "paged_attention_general_mma")
+            return
+        nsplit, chunk, part_o, part_ml = 1, 0, None, None
+        if (k_cache.dtype == torch.bfloat16 and ctx.max_q_len * (nq // nkv) <= self.GENERAL_ROWS and not window
+                and self.split_general_attention):
+            nsplit, chunk = self.attention_split(n, nkv, ctx.kv_bound, max_slices=64)
+            if nsplit > 1:
+                part_o = ctx.workspace.get("attn.general_part_o", n * nkv * nsplit * self.GENERAL_ROWS, dv,
+                                           torch.float32, reserve=0)
+                part_ml = ctx.workspace.get("attn.general_part_ml", n * nkv * nsplit * self.GENERAL_ROWS, 2,
+                                            torch.float32, reserve=0)
         self._check(self.lib.srlm_paged_attention_general(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), dtype_code(k_cache.dtype), dtype_code(out.dtype),
             _ptr(block_table), C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks),
-            C.c_int(ctx.n_entries), C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
-            C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), _stream()), "paged_attention_general")
+            C.c_int(n), C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
+            C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), C.c_int(nsplit), C.c_int(chunk),
+            _ptr(part_o), _ptr(part_ml), _stream()), "paged_attention_general")
+        if nsplit > 1:
+            self.launches += 1           # the kernel that adds the slices
 
     def attention_bias_append(self, proj, bias, q_out, k_cache, v_cache, kv_slot, nq, nkv, dk, dv, v_keep=None,
                               lam=None, mix_mode=0, write_kv=True):
