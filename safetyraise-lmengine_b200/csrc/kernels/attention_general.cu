@@ -175,33 +175,42 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
   }
 }
 
-// One warp per (entry, KV head, row): adds the slices' sums in slice order.
+// One block per (entry, KV head, row): adds the slices' sums in slice order.  rows_padded: rows a slice holds
+// per (entry, KV head) in part_o / part_ml (a multiple of 16).  Each slice's weight exp(m_s - M) is formed once.
+constexpr int kMaxSlices = 64;
+
 template <typename TO>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        TO* __restrict__ out, const int* __restrict__ cu_q, int n_entries, int nq,
-                                       int nkv, int dv, int nsplit) {
-  const int lane = threadIdx.x & 31;
-  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= (long long)n_entries * nkv * kRows) return;
-  const int r = (int)(w % kRows), kvh = (int)((w / kRows) % nkv), e = (int)(w / ((long long)kRows * nkv));
+                                       int nkv, int dv, int nsplit, int rows_padded) {
+  __shared__ float w[kMaxSlices];
+  __shared__ float inv_l;
+  const long long b = blockIdx.x;
+  const int r = (int)(b % rows_padded), kvh = (int)((b / rows_padded) % nkv), e = (int)(b / ((long long)rows_padded * nkv));
   const int G = nq / nkv, t0 = cu_q[e], rows = (cu_q[e + 1] - t0) * G;
   if (r >= rows) return;
-  const size_t first = (((size_t)e * nkv + kvh) * nsplit) * kRows + r;
-  float M = -CUDART_INF_F;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_ml[(first + (size_t)s * kRows) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < nsplit; ++s) {
-    const float ms = part_ml[(first + (size_t)s * kRows) * 2];
-    if (ms != -CUDART_INF_F) L += part_ml[(first + (size_t)s * kRows) * 2 + 1] * expf(ms - M);
-  }
-  TO* o = out + ((size_t)(t0 + r / G) * nq + kvh * G + r % G) * dv;
-  for (int col = lane; col < dv; col += 32) {
-    float a = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-      const float ms = part_ml[(first + (size_t)s * kRows) * 2];
-      if (ms != -CUDART_INF_F) a += part_o[(first + (size_t)s * kRows) * dv + col] * expf(ms - M);
+  const size_t first = (((size_t)e * nkv + kvh) * nsplit) * rows_padded + r;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float M = -CUDART_INF_F;
+    for (int s = lane; s < nsplit; s += 32) M = fmaxf(M, part_ml[(first + (size_t)s * rows_padded) * 2]);
+    M = warp_max(M);
+    float L = 0.f;
+    for (int s = lane; s < nsplit; s += 32) {
+      const float ms = part_ml[(first + (size_t)s * rows_padded) * 2];
+      const float ws = ms != -CUDART_INF_F ? expf(ms - M) : 0.f;
+      w[s] = ws;
+      L += part_ml[(first + (size_t)s * rows_padded) * 2 + 1] * ws;
     }
-    o[col] = from_float<TO>(a / L);
+    L = warp_sum(L);
+    if (lane == 0) inv_l = 1.f / L;
+  }
+  __syncthreads();
+  TO* o = out + ((size_t)(t0 + r / G) * nq + kvh * G + r % G) * dv;
+  for (int col = threadIdx.x; col < dv; col += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < nsplit; ++s) a += part_o[(first + (size_t)s * rows_padded) * dv + col] * w[s];
+    o[col] = from_float<TO>(a * inv_l);
   }
 }
 
@@ -263,9 +272,9 @@ static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, 
   }
 #undef SRLM_GENERAL_CASE
   if (nsplit > 1) {
-    const long long warps = (long long)n_entries * nkv * kRows;
-    attention_merge_kernel<TO><<<(unsigned)((warps + 3) / 4), 128, 0, stream>>>(part_o, part_ml, (TO*)out, cu_q,
-                                                                                n_entries, nq, nkv, dv, nsplit);
+    const long long blocks = (long long)n_entries * nkv * kRows;
+    attention_merge_kernel<TO><<<(unsigned)blocks, 128, 0, stream>>>(part_o, part_ml, (TO*)out, cu_q, n_entries, nq,
+                                                                     nkv, dv, nsplit, kRows);
   }
   return launched();
 }
@@ -295,6 +304,7 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
   if (nsplit > 1 && (tiles != 1 || kv_chunk <= 0 || kv_chunk % kKeys || !part_o || !part_ml))
     return refuse(ST_BAD_SIZE, "paged_attention_general: %d slices of %d keys need entries of at most %d rows, slices "
                   "of whole key blocks and a workspace", nsplit, kv_chunk, kRows);
+  if (nsplit > kMaxSlices) return refuse(ST_BAD_SIZE, "paged_attention_general: at most %d slices", kMaxSlices);
   if (nsplit < 1) nsplit = 1;
   dim3 grid((unsigned)(nsplit > 1 ? nsplit : tiles), (unsigned)nkv, (unsigned)n_entries);
   int vpl = 1;
@@ -335,5 +345,24 @@ extern "C" int srlm_attention_bias_append(const void* proj, int proj_dtype, long
   else if (proj_dtype == DT_BF16 && cache_dtype == DT_BF16) SRLM_APPEND(bf16, bf16);
   else return refuse(ST_BAD_DTYPE, "attention_bias_append: projection dtype %d with cache dtype %d", proj_dtype, cache_dtype);
 #undef SRLM_APPEND
+  return launched();
+}
+
+// Adds the slices that a sliced attention kernel left in part_o [.., rows_padded, dv] / part_ml [.., rows_padded, 2].
+extern "C" int srlm_attention_general_merge(const float* part_o, const float* part_ml, void* out, int out_dtype,
+                                            const int* cu_q, int n_entries, int nq, int nkv, int dv, int nsplit,
+                                            int rows_padded, cudaStream_t stream) {
+  if (n_entries <= 0 || nsplit <= 1) return ST_OK;
+  if (nsplit > kMaxSlices || rows_padded <= 0)
+    return refuse(ST_BAD_SIZE, "attention_general_merge: %d slices (at most %d), %d rows", nsplit, kMaxSlices, rows_padded);
+  const long long blocks = (long long)n_entries * nkv * rows_padded;
+  if (out_dtype == DT_F32)
+    attention_merge_kernel<float><<<(unsigned)blocks, 128, 0, stream>>>(part_o, part_ml, (float*)out, cu_q, n_entries, nq,
+                                                                        nkv, dv, nsplit, rows_padded);
+  else if (out_dtype == DT_BF16)
+    attention_merge_kernel<bf16><<<(unsigned)blocks, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, cu_q, n_entries, nq,
+                                                                       nkv, dv, nsplit, rows_padded);
+  else
+    return refuse(ST_BAD_DTYPE, "attention_general_merge: output dtype %d", out_dtype);
   return launched();
 }

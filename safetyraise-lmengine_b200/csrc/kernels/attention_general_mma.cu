@@ -36,6 +36,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src, bool full) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int n = full ? 16 : 0;                               // 0: sixteen zero bytes, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+
 template <typename TO, int NT>       // NT: 8-column tiles of the block's slab of values (8 or 16)
 __global__ void __launch_bounds__(kMmaWarps * 32)
 paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
@@ -43,7 +51,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
                                    const int* __restrict__ block_table, int table_stride,
                                    const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                                    const float* __restrict__ sinks, int nq, int nkv, int dk, int dv, int page_size,
-                                   float scale, int window) {
+                                   float scale, int window, int nbuf) {
   constexpr int DVT = 8 * NT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int slabs = dv / DVT;
@@ -56,8 +64,11 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   const int ks = dk + kPad;                                 // row strides in elements; rows stay 16-byte aligned
   const int vs = v_cache ? DVT + kPad : ks;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);            // [64][dk + 8]
-  bf16* k_s = q_s + kMmaRows * ks;                          // [64][dk + 8]
-  bf16* v_s = v_cache ? k_s + kMmaKeys * ks : k_s + slab * DVT;   // [64][DVT + 8], or the slab's columns of the keys
+  // nbuf = 2 when two tiles of keys (and values) fit beside the queries: the next tile is fetched (cp.async)
+  // while this one is worked on; nbuf = 1: fetched, waited for, worked on
+  bf16* k_s = q_s + kMmaRows * ks;                          // [nbuf][64][dk + 8]
+  bf16* v_s = v_cache ? k_s + nbuf * kMmaKeys * ks : k_s + slab * DVT;   // [nbuf][64][DVT + 8], or the slab's columns of the keys
+  const int k_tile = kMmaKeys * ks, v_tile = v_cache ? kMmaKeys * vs : k_tile;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int start = kv_len - q_len;
   const int* table = block_table + (size_t)e * table_stride;
@@ -92,27 +103,38 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   const int first_key = window > 0 ? max(0, min_pos - window + 1) : 0;
   const int kvec = dk / 8, vvec = DVT / 8;
 
-  for (int jb = (first_key / kMmaKeys) * kMmaKeys; jb <= max_pos; jb += kMmaKeys) {
-    __syncthreads();
+  auto fetch = [&](int jb, int buf) {
     for (int idx = tid; idx < kMmaKeys * kvec; idx += blockDim.x) {
       const int jj = idx / kvec, c = idx - jj * kvec, j = jb + jj;
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (j <= max_pos) {
-        const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
-        v = *reinterpret_cast<const uint4*>(k_cache + rowi * dk + c * 8);
-      }
-      *reinterpret_cast<uint4*>(k_s + jj * ks + c * 8) = v;
+      const bool there = j <= max_pos;
+      const size_t rowi = there ? ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size) : 0;
+      cp_async_16(k_s + buf * k_tile + jj * ks + c * 8, k_cache + rowi * dk + c * 8, there);
     }
     if (v_cache) {
       for (int idx = tid; idx < kMmaKeys * vvec; idx += blockDim.x) {
         const int jj = idx / vvec, c = idx - jj * vvec, j = jb + jj;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (j <= max_pos) {
-          const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
-          v = *reinterpret_cast<const uint4*>(v_cache + rowi * dv + slab * DVT + c * 8);
-        }
-        *reinterpret_cast<uint4*>(v_s + jj * vs + c * 8) = v;
+        const bool there = j <= max_pos;
+        const size_t rowi = there ? ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size) : 0;
+        cp_async_16(v_s + buf * v_tile + jj * vs + c * 8, v_cache + rowi * dv + slab * DVT + c * 8, there);
       }
+    }
+    cp_async_commit();
+  };
+  const int jb0 = (first_key / kMmaKeys) * kMmaKeys;
+  if (nbuf == 2 && jb0 <= max_pos) fetch(jb0, 0);
+  int buf = 0;
+  for (int jb = jb0; jb <= max_pos; jb += kMmaKeys) {
+    if (nbuf == 2) {
+      if (jb + kMmaKeys <= max_pos) {
+        fetch(jb + kMmaKeys, buf ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+    } else {
+      __syncthreads();                                      // the tile is no longer read
+      fetch(jb, 0);
+      cp_async_wait<0>();
     }
     __syncthreads();
 
@@ -123,7 +145,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
 #pragma unroll
       for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
     const bf16* qa = q_s + (warp * 16 + (lane & 15)) * ks + (lane >> 4) * 8;
-    const bf16* kb = k_s + ((lane & 7) + (lane >> 4) * 8) * ks + ((lane >> 3) & 1) * 8;
+    const bf16* kb = k_s + buf * k_tile + ((lane & 7) + (lane >> 4) * 8) * ks + ((lane >> 3) & 1) * 8;
     for (int k0 = 0; k0 < dk; k0 += 16) {
       uint32_t a[4];
       ldmatrix_x4(a, qa + k0);
@@ -180,7 +202,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
     }
 
     // O += P V for the slab
-    const bf16* vb = v_s + (lane & 15) * vs + (lane >> 4) * 8;
+    const bf16* vb = v_s + buf * v_tile + (lane & 15) * vs + (lane >> 4) * 8;
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       uint32_t a[4];
@@ -195,6 +217,10 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
         mma_bf16(o[2 * n2], a, b[0], b[1]);
         mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
       }
+    }
+    if (nbuf == 2) {
+      __syncthreads();                                      // before the next fetch goes into this tile's twin
+      buf ^= 1;
     }
   }
 
@@ -212,16 +238,217 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   }
 }
 
+// ---- decode steps: entries of at most 16 rows -------------------------------------------------------------
+// A block takes one slice of an entry's keys for one KV head.  Its four warps walk the same tiles of 32 keys
+// (fetched with cp.async, two tiles in flight) and all form the same S and the same softmax for the 16 rows;
+// each warp owns a quarter of the value columns (NTW tiles of 8), so a wide value needs no second pass over
+// the keys, which is what a decode step is bound by.  nsplit > 1: the slices' unnormalised sums go to
+// part_o / part_ml (the entry's rows padded to whole tiles of 16 per slice) and attention_general.cu's merge
+// kernel adds them.  An entry of more than 16 rows (many query heads per KV head, or a few tokens) is several
+// blocks, each walking the slice again: the second reading comes from L2.
+constexpr int kDecKeys = 32;
+
+template <typename TO, int NTW>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
+                                      const bf16* __restrict__ v_cache, TO* __restrict__ out,
+                                      const int* __restrict__ block_table, int table_stride,
+                                      const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
+                                      const float* __restrict__ sinks, int nq, int nkv, int dk, int dv,
+                                      int page_size, float scale, int window, int nsplit, int kv_chunk,
+                                      float* __restrict__ part_o, float* __restrict__ part_ml, int row_tiles) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int e = blockIdx.z, kvh = blockIdx.y / row_tiles, slice = blockIdx.x;
+  const int r0 = (blockIdx.y % row_tiles) * 16;             // the block's 16 rows of the entry's q_len * G
+  const int G = nq / nkv;
+  const int t0 = cu_q[e], q_len = cu_q[e + 1] - t0, kv_len = kv_lens[e];
+  const int rows = q_len * G;
+  if (r0 >= rows) return;
+  const int ks = dk + kPad, vs = v_cache ? dv + kPad : ks;
+  bf16* q_s = reinterpret_cast<bf16*>(smem_raw);            // [16][dk + 8]
+  bf16* k_s = q_s + 16 * ks;                                // [2][32][dk + 8]
+  bf16* v_s = v_cache ? k_s + 2 * kDecKeys * ks : k_s;      // [2][32][dv + 8], or the keys
+  const int k_tile = kDecKeys * ks, v_tile = v_cache ? kDecKeys * vs : k_tile;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int start = kv_len - q_len;
+  const int* table = block_table + (size_t)e * table_stride;
+
+  for (int idx = tid; idx < 16 * dk; idx += blockDim.x) {
+    const int r = idx / dk, d = idx - r * dk, row = r0 + r;
+    const float v = row < rows ? q[((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dk + d] : 0.f;
+    q_s[r * ks + d] = __float2bfloat16_rn(v);
+  }
+  float m[2], l[2];
+  int pos[2], first[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = r0 + (lane >> 2) + 8 * i;
+    const bool live = row < rows;
+    pos[i] = live ? start + row / G : -1;
+    first[i] = (window > 0 && live) ? max(0, pos[i] - window + 1) : 0;
+    const bool with_sink = sinks && slice == 0;             // the sink counts once
+    m[i] = with_sink ? sinks[kvh * G + (live ? row % G : 0)] : -CUDART_INF_F;
+    l[i] = with_sink ? 1.f : 0.f;
+  }
+  float o[NTW][4];
+#pragma unroll
+  for (int n = 0; n < NTW; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+  const int max_pos = start + (min(rows, r0 + 16) - 1) / G;
+  int first_key = window > 0 ? max(0, start + r0 / G - window + 1) : 0;
+  int last_key = max_pos;
+  if (nsplit > 1) {
+    first_key = max(first_key, slice * kv_chunk);
+    last_key = min(last_key, (slice + 1) * kv_chunk - 1);
+  }
+  const int jb0 = (first_key / kDecKeys) * kDecKeys;
+  const int kvec = dk / 8, vvec = dv / 8;
+  auto fetch = [&](int jb, int buf) {
+    for (int idx = tid; idx < kDecKeys * kvec; idx += blockDim.x) {
+      const int jj = idx / kvec, c = idx - jj * kvec, j = jb + jj;
+      const bool there = j <= last_key;
+      const size_t rowi = there ? ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size) : 0;
+      cp_async_16(k_s + buf * k_tile + jj * ks + c * 8, k_cache + rowi * dk + c * 8, there);
+    }
+    if (v_cache) {
+      for (int idx = tid; idx < kDecKeys * vvec; idx += blockDim.x) {
+        const int jj = idx / vvec, c = idx - jj * vvec, j = jb + jj;
+        const bool there = j <= last_key;
+        const size_t rowi = there ? ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size) : 0;
+        cp_async_16(v_s + buf * v_tile + jj * vs + c * 8, v_cache + rowi * dv + c * 8, there);
+      }
+    }
+    cp_async_commit();
+  };
+  if (jb0 <= last_key) fetch(jb0, 0);
+  int buf = 0;
+  for (int jb = jb0; jb <= last_key; jb += kDecKeys, buf ^= 1) {
+    if (jb + kDecKeys <= last_key) {
+      fetch(jb + kDecKeys, buf ^ 1);                        // the tile after this one, into the other buffer
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    float s[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s[n][c] = 0.f;
+    const bf16* qa = q_s + (lane & 15) * ks + (lane >> 4) * 8;
+    const bf16* kb = k_s + buf * k_tile + ((lane & 7) + (lane >> 4) * 8) * ks + ((lane >> 3) & 1) * 8;
+    for (int k0 = 0; k0 < dk; k0 += 16) {
+      uint32_t a[4];
+      ldmatrix_x4(a, qa + k0);
+#pragma unroll
+      for (int n2 = 0; n2 < 2; ++n2) {
+        uint32_t b[4];
+        ldmatrix_x4(b, kb + n2 * 16 * ks + k0);
+        mma_bf16(s[2 * n2], a, b[0], b[1]);
+        mma_bf16(s[2 * n2 + 1], a, b[2], b[3]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float mx = -CUDART_INF_F;
+#pragma unroll
+      for (int n = 0; n < 4; ++n)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int j = jb + n * 8 + (lane & 3) * 2 + c;
+          const bool valid = j <= pos[i] && j >= first[i] && j >= first_key && j <= last_key;
+          const float v = valid ? s[n][2 * i + c] * scale : -CUDART_INF_F;
+          s[n][2 * i + c] = v;
+          mx = fmaxf(mx, v);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m[i], mx);
+      float alpha = 1.f, sum = 0.f;
+      if (m_new != -CUDART_INF_F) {
+        alpha = expf(m[i] - m_new);
+#pragma unroll
+        for (int n = 0; n < 4; ++n)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const float p = expf(s[n][2 * i + c] - m_new);
+            s[n][2 * i + c] = p;
+            sum += p;
+          }
+      } else {
+#pragma unroll
+        for (int n = 0; n < 4; ++n) s[n][2 * i] = s[n][2 * i + 1] = 0.f;
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      l[i] = l[i] * alpha + sum;
+      m[i] = m_new;
+#pragma unroll
+      for (int n = 0; n < NTW; ++n) {
+        o[n][2 * i] *= alpha;
+        o[n][2 * i + 1] *= alpha;
+      }
+    }
+    const bf16* vb = v_s + buf * v_tile + (lane & 15) * vs + warp * (NTW * 8) + (lane >> 4) * 8;
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+      uint32_t a[4];
+      a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+      a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int n2 = 0; n2 < NTW / 2; ++n2) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, vb + kk * 16 * vs + n2 * 16);
+        mma_bf16(o[2 * n2], a, b[0], b[1]);
+        mma_bf16(o[2 * n2 + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();                                         // before the next fetch overwrites this buffer's twin
+  }
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int row = r0 + (lane >> 2) + 8 * i;
+    if (row >= rows) continue;
+    const int col0 = warp * (NTW * 8) + (lane & 3) * 2;
+    if (nsplit > 1) {
+      const size_t slab = (((size_t)e * nkv + kvh) * nsplit + slice) * (16 * row_tiles) + row;
+#pragma unroll
+      for (int n = 0; n < NTW; ++n) {
+        part_o[slab * dv + col0 + n * 8] = o[n][2 * i];
+        part_o[slab * dv + col0 + n * 8 + 1] = o[n][2 * i + 1];
+      }
+      if (warp == 0 && (lane & 3) == 0) {
+        part_ml[slab * 2] = m[i];
+        part_ml[slab * 2 + 1] = l[i];
+      }
+    } else {
+      const float inv = 1.f / l[i];
+      TO* dst = out + ((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dv + col0;
+#pragma unroll
+      for (int n = 0; n < NTW; ++n) {
+        dst[n * 8] = from_float<TO>(o[n][2 * i] * inv);
+        dst[n * 8 + 1] = from_float<TO>(o[n][2 * i + 1] * inv);
+      }
+    }
+  }
+}
+
 template <typename TO, int NT>
 static int launch_mma(dim3 grid, size_t smem, cudaStream_t stream, const float* q, const void* k_cache,
                       const void* v_cache, void* out, const int* block_table, int table_stride, const int* cu_q,
                       const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
-                      float scale, int window) {
+                      float scale, int window, int nbuf) {
   auto kern = paged_attention_general_mma_kernel<TO, NT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   kern<<<grid, kMmaWarps * 32, smem, stream>>>(q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out, block_table,
                                                table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale,
-                                               window);
+                                               window, nbuf);
   return launched();
 }
 
@@ -256,11 +483,67 @@ extern "C" int srlm_paged_attention_general_mma(const float* q, const void* k_ca
   const long long y = (long long)nkv * (dv / slab);
   if (n_entries > 65535 || y > 65535) return refuse(ST_BAD_SIZE, "paged_attention_general_mma: %d entries", n_entries);
   dim3 grid((unsigned)tiles, (unsigned)y, (unsigned)n_entries);
-  const size_t smem = (size_t)2 * kMmaRows * (dk + kPad) * 2 + (v_cache ? (size_t)kMmaKeys * (slab + kPad) * 2 : 0);
+  const size_t q_bytes = (size_t)kMmaRows * (dk + kPad) * 2;
+  const size_t tile_bytes = (size_t)kMmaKeys * (dk + kPad) * 2 + (v_cache ? (size_t)kMmaKeys * (slab + kPad) * 2 : 0);
+  // two tiles in flight when that still leaves room for two blocks an SM
+  const int nbuf = q_bytes + 2 * tile_bytes <= 100 * 1024 ? 2 : 1;
+  const size_t smem = q_bytes + nbuf * tile_bytes;
 #define SRLM_MMA_ARGS grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_lens, sinks, nq, \
-                      nkv, dk, dv, page_size, scale, window
+                      nkv, dk, dv, page_size, scale, window, nbuf
   if (out_dtype == DT_F32) return slab == 128 ? launch_mma<float, 16>(SRLM_MMA_ARGS) : launch_mma<float, 8>(SRLM_MMA_ARGS);
   if (out_dtype == DT_BF16) return slab == 128 ? launch_mma<bf16, 16>(SRLM_MMA_ARGS) : launch_mma<bf16, 8>(SRLM_MMA_ARGS);
 #undef SRLM_MMA_ARGS
   return refuse(ST_BAD_DTYPE, "paged_attention_general_mma: output dtype %d", out_dtype);
+}
+
+// Decode steps (entries of a few rows each) over a bfloat16 cache: value size 64, 128, 256 or 512, key size
+// a multiple of 16.  With nsplit > 1 the caller then runs srlm_attention_general_merge over part_o / part_ml.
+extern "C" int srlm_attention_general_decode_takes(int dk, int dv, int values_from_keys) {
+  if (dk <= 0 || dk % 16 || (dv != 64 && dv != 128 && dv != 256 && dv != 512) || (values_from_keys && dv > dk)) return 0;
+  const size_t smem = (size_t)(16 + 2 * kDecKeys) * (dk + kPad) * 2 + (values_from_keys ? 0 : (size_t)2 * kDecKeys * (dv + kPad) * 2);
+  return smem <= 220 * 1024 ? 1 : 0;
+}
+
+extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k_cache, const void* v_cache, void* out,
+                                                   int out_dtype, const int* block_table, int table_stride,
+                                                   const int* cu_q, const int* kv_lens, const float* sinks,
+                                                   int n_entries, int max_q_len, int nq, int nkv, int dk, int dv,
+                                                   int page_size, float scale, int window, int nsplit, int kv_chunk,
+                                                   float* part_o, float* part_ml, cudaStream_t stream) {
+  if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || !srlm_attention_general_decode_takes(dk, dv, v_cache ? 0 : 1))
+    return refuse(ST_BAD_SIZE, "paged_attention_general_decode: nq=%d nkv=%d dk=%d dv=%d rows=%d", nq, nkv, dk, dv,
+                  max_q_len * (nq / (nkv > 0 ? nkv : 1)));
+  if (nsplit < 1) nsplit = 1;
+  if (nsplit > 1 && (kv_chunk <= 0 || kv_chunk % kDecKeys || !part_o || !part_ml))
+    return refuse(ST_BAD_SIZE, "paged_attention_general_decode: %d slices of %d keys need a workspace", nsplit, kv_chunk);
+  if ((((uintptr_t)k_cache | (uintptr_t)v_cache) & 15) != 0)
+    return refuse(ST_BAD_ALIGN, "paged_attention_general_decode: the pools must be 16-byte aligned");
+  const int row_tiles = (int)(((long long)max_q_len * (nq / nkv) + 15) / 16);
+  if (n_entries > 65535 || (long long)nkv * row_tiles > 65535)
+    return refuse(ST_BAD_SIZE, "paged_attention_general_decode: %d entries, %d row tiles", n_entries, row_tiles);
+  dim3 grid((unsigned)nsplit, (unsigned)(nkv * row_tiles), (unsigned)n_entries);
+  const size_t smem = (size_t)(16 + 2 * kDecKeys) * (dk + kPad) * 2 + (v_cache ? (size_t)2 * kDecKeys * (dv + kPad) * 2 : 0);
+#define SRLM_DEC(TO, NTW)                                                                                          \
+  do {                                                                                                             \
+    auto kern = paged_attention_general_decode_kernel<TO, NTW>;                                                    \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    kern<<<grid, kMmaWarps * 32, smem, stream>>>(q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out,          \
+                                                 block_table, table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, \
+                                                 page_size, scale, window, nsplit, kv_chunk, part_o, part_ml,      \
+                                                 row_tiles);                                                       \
+  } while (0)
+#define SRLM_DEC_SIZES(TO)                                \
+  do {                                                    \
+    if (dv == 64) SRLM_DEC(TO, 2);                        \
+    else if (dv == 128) SRLM_DEC(TO, 4);                  \
+    else if (dv == 256) SRLM_DEC(TO, 8);                  \
+    else SRLM_DEC(TO, 16);                                \
+  } while (0)
+  if (out_dtype == DT_F32) SRLM_DEC_SIZES(float);
+  else if (out_dtype == DT_BF16) SRLM_DEC_SIZES(bf16);
+  else return refuse(ST_BAD_DTYPE, "paged_attention_general_decode: output dtype %d", out_dtype);
+#undef SRLM_DEC_SIZES
+#undef SRLM_DEC
+  return launched();
 }

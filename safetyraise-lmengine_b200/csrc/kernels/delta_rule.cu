@@ -95,72 +95,115 @@ __global__ void delta_conv_carry_kernel(const TP* __restrict__ proj, long long l
 }
 
 // Block: 32 columns of one head's S for one entry; a column is shared by 8 lanes, lane l holding rows
-// l, l + 8, ... (RPL of them).  The next token's operands are fetched while this token's are used.
+// 32 j + 4 l + {0..3} (RPL of them, four consecutive at a time so that shared memory is read 16 bytes a
+// lane).  The entry's tokens come through shared memory in chunks of 16, the next chunk fetched (cp.async)
+// while this one is worked on.  Per token the dependent chain is one round of partial sums over the OLD
+// state and one round of shuffles: with a = k . S and b = q . S (both over the state before the token)
+// and c = q . k,
+//     u = beta (v - g a),   S <- g S + k u,   o = g b + c u      ( = q . S after the write )
+// so the three sums are reduced side by side and the state update is one FMA deep.
+constexpr int kChunk = 16;
+
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src));
+}
+
 template <int RPL>
 __global__ void __launch_bounds__(kColumnsPerBlock* kLanesPerColumn)
 delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                         float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ slots, float* __restrict__ o_out, int H, int G, int dk, int dv) {
+  constexpr int DKP = RPL * kLanesPerColumn;                 // rows held in shared memory (zero beyond dk)
+  constexpr int ROW = 2 * DKP + kColumnsPerBlock + 4;        // k | q | v of the block's columns | beta, g, -, -
+  extern __shared__ __align__(16) float stage[];            // [2][kChunk][ROW]
   const int e = blockIdx.z, h = blockIdx.y;
-  const int col = blockIdx.x * kColumnsPerBlock + threadIdx.x / kLanesPerColumn;
-  const int l = threadIdx.x % kLanesPerColumn;
+  const int cg = threadIdx.x / kLanesPerColumn, l = threadIdx.x % kLanesPerColumn;
+  const int col = blockIdx.x * kColumnsPerBlock + cg;
   const bool live = col < dv;
   const int kh = h / (H / G);
   const int C = 2 * G * dk + H * dv;
-  const int t0 = cu_q[e], t1 = cu_q[e + 1];
+  const int t0 = cu_q[e], n_tok = cu_q[e + 1] - t0;
   float* S_col = state + (size_t)slots[e] * state_stride + ((size_t)h * dv + (live ? col : 0)) * dk;
-  float S[RPL], kc[RPL], qc[RPL], kn[RPL], qn[RPL];
+  float S[RPL];
 #pragma unroll
   for (int i = 0; i < RPL; ++i) {
-    const int r = l + kLanesPerColumn * i;
+    const int r = (i >> 2) * 32 + 4 * l + (i & 3);
     S[i] = (live && r < dk) ? S_col[r] : 0.f;
-    kn[i] = qn[i] = 0.f;
   }
-  float vc, bc, gc, vn = 0.f, bn = 0.f, gn = 0.f;
-#define SRLM_DELTA_FETCH(t)                                                          \
-  do {                                                                               \
-    const float* row = qkv + (size_t)(t) * C;                                        \
-    _Pragma("unroll") for (int i = 0; i < RPL; ++i) {                                \
-      const int r = l + kLanesPerColumn * i;                                         \
-      qn[i] = r < dk ? row[(size_t)kh * dk + r] : 0.f;                               \
-      kn[i] = r < dk ? row[(size_t)(G + kh) * dk + r] : 0.f;                         \
-    }                                                                                \
-    vn = live ? row[(size_t)2 * G * dk + (size_t)h * dv + col] : 0.f;                \
-    bn = beta[(size_t)(t) * H + h];                                                  \
-    gn = decay[(size_t)(t) * H + h];                                                 \
-  } while (0)
-  if (t0 < t1) SRLM_DELTA_FETCH(t0);
-  for (int t = t0; t < t1; ++t) {
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) { kc[i] = kn[i]; qc[i] = qn[i]; }
-    vc = vn; bc = bn; gc = gn;
-    if (t + 1 < t1) SRLM_DELTA_FETCH(t + 1);
-    float ks = 0.f;
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      S[i] *= gc;
-      ks += kc[i] * S[i];
+  for (int idx = threadIdx.x; idx < 2 * kChunk * ROW; idx += blockDim.x) stage[idx] = 0.f;
+  __syncthreads();
+  const int col0 = blockIdx.x * kColumnsPerBlock;
+  auto fetch = [&](int chunk, int buf) {
+    const int base = chunk * kChunk, n = min(kChunk, n_tok - base);
+    float* st = stage + buf * kChunk * ROW;
+    for (int idx = threadIdx.x; idx < n * dk; idx += blockDim.x) {
+      const int i = idx / dk, r = idx - i * dk;
+      const float* row = qkv + (size_t)(t0 + base + i) * C;
+      cp_async_4(st + i * ROW + r, row + (size_t)(G + kh) * dk + r);            // k
+      cp_async_4(st + i * ROW + DKP + r, row + (size_t)kh * dk + r);            // q
     }
-    ks += __shfl_xor_sync(0xffffffffu, ks, 1);
-    ks += __shfl_xor_sync(0xffffffffu, ks, 2);
-    ks += __shfl_xor_sync(0xffffffffu, ks, 4);
-    const float u = bc * (vc - ks);
-    float o = 0.f;
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      S[i] += kc[i] * u;
-      o += qc[i] * S[i];
+    for (int idx = threadIdx.x; idx < n * kColumnsPerBlock; idx += blockDim.x) {
+      const int i = idx / kColumnsPerBlock, c = idx - i * kColumnsPerBlock;
+      if (col0 + c < dv)
+        cp_async_4(st + i * ROW + 2 * DKP + c, qkv + (size_t)(t0 + base + i) * C + 2 * G * dk + (size_t)h * dv + col0 + c);
     }
-    o += __shfl_xor_sync(0xffffffffu, o, 1);
-    o += __shfl_xor_sync(0xffffffffu, o, 2);
-    o += __shfl_xor_sync(0xffffffffu, o, 4);
-    if (live && l == 0) o_out[((size_t)t * H + h) * dv + col] = o;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      cp_async_4(st + i * ROW + 2 * DKP + kColumnsPerBlock, beta + (size_t)(t0 + base + i) * H + h);
+      cp_async_4(st + i * ROW + 2 * DKP + kColumnsPerBlock + 1, decay + (size_t)(t0 + base + i) * H + h);
+    }
+    asm volatile("cp.async.commit_group;" ::);
+  };
+  const int chunks = (n_tok + kChunk - 1) / kChunk;
+  if (chunks > 0) fetch(0, 0);
+  for (int c = 0; c < chunks; ++c) {
+    const int buf = c & 1;
+    if (c + 1 < chunks) {
+      fetch(c + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::);
+    }
+    __syncthreads();
+    const float* st = stage + buf * kChunk * ROW;
+    const int n = min(kChunk, n_tok - c * kChunk);
+    for (int i = 0; i < n; ++i) {
+      const float* row = st + i * ROW;
+      float kk[RPL], qq[RPL];
+#pragma unroll
+      for (int j = 0; j < RPL / 4; ++j) {
+        const float4 kv = *reinterpret_cast<const float4*>(row + j * 32 + 4 * l);
+        const float4 qv = *reinterpret_cast<const float4*>(row + DKP + j * 32 + 4 * l);
+        kk[4 * j] = kv.x; kk[4 * j + 1] = kv.y; kk[4 * j + 2] = kv.z; kk[4 * j + 3] = kv.w;
+        qq[4 * j] = qv.x; qq[4 * j + 1] = qv.y; qq[4 * j + 2] = qv.z; qq[4 * j + 3] = qv.w;
+      }
+      const float v = row[2 * DKP + cg], bt = row[2 * DKP + kColumnsPerBlock], g = row[2 * DKP + kColumnsPerBlock + 1];
+      float a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f}, c4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < RPL; ++j) {                        // four running sums each: no chain of RPL additions
+        a4[j & 3] += kk[j] * S[j];
+        b4[j & 3] += qq[j] * S[j];
+        c4[j & 3] += qq[j] * kk[j];
+      }
+      float a = (a4[0] + a4[1]) + (a4[2] + a4[3]), b = (b4[0] + b4[1]) + (b4[2] + b4[3]);
+      float cc = (c4[0] + c4[1]) + (c4[2] + c4[3]);
+#pragma unroll
+      for (int off = 1; off < kLanesPerColumn; off <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, off);
+        b += __shfl_xor_sync(0xffffffffu, b, off);
+        cc += __shfl_xor_sync(0xffffffffu, cc, off);
+      }
+      const float u = bt * (v - g * a);
+#pragma unroll
+      for (int j = 0; j < RPL; ++j) S[j] = g * S[j] + kk[j] * u;
+      if (live && l == 0) o_out[((size_t)(t0 + c * kChunk + i) * H + h) * dv + col] = g * b + cc * u;
+    }
+    __syncthreads();                                         // the chunk is done with before its buffer is fetched into
   }
-#undef SRLM_DELTA_FETCH
   if (live) {
 #pragma unroll
     for (int i = 0; i < RPL; ++i) {
-      const int r = l + kLanesPerColumn * i;
+      const int r = (i >> 2) * 32 + 4 * l + (i & 3);
       if (r < dk) S_col[r] = S[i];
     }
   }
@@ -228,9 +271,14 @@ extern "C" int srlm_delta_recurrence(const float* qkv, const float* beta, const 
   dim3 grid((dv + kColumnsPerBlock - 1) / kColumnsPerBlock, H, n_entries);
   const int threads = kColumnsPerBlock * kLanesPerColumn;
   const int rpl = (dk + kLanesPerColumn - 1) / kLanesPerColumn;
-#define SRLM_DELTA_CASE(R)                                                                                            \
-  delta_recurrence_kernel<R><<<grid, threads, 0, stream>>>(qkv, beta, decay, state, state_stride, cu_q, slots, o_out, \
-                                                           H, G, dk, dv)
+#define SRLM_DELTA_CASE(R)                                                                                       \
+  do {                                                                                                           \
+    const size_t smem = (size_t)2 * kChunk * (2 * R * kLanesPerColumn + kColumnsPerBlock + 4) * sizeof(float);   \
+    if (smem > 48 * 1024)                                                                                        \
+      cudaFuncSetAttribute(delta_recurrence_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    delta_recurrence_kernel<R><<<grid, threads, smem, stream>>>(qkv, beta, decay, state, state_stride, cu_q,     \
+                                                                slots, o_out, H, G, dk, dv);                     \
+  } while (0)
   if (rpl <= 4) SRLM_DELTA_CASE(4);
   else if (rpl <= 8) SRLM_DELTA_CASE(8);
   else if (rpl <= 16) SRLM_DELTA_CASE(16);

@@ -763,17 +763,46 @@ class KernelLibrary:
         k_cache [pages, nkv, page_size, dk]; out [T, nq * dv], float32 or the cache's dtype; sinks float32
         [nq] or None: one more term exp(sink) in each head's softmax denominator.
 
-        A bfloat16 cache and more than 16 rows in some entry (prompts, portions, mixed steps): the tensor-core
-        form (attention_general_mma.cu) when it takes the sizes.
-        When every entry has at most 16 rows (decode steps) and the cache is bfloat16, the keys are cut into
-        slices with a block each, as many as run at the same time, and a second kernel adds them; the
-        float32 path keeps one block per entry and KV head, whose sums do not depend on the batch."""
+        A bfloat16 cache: the tensor-core forms (attention_general_mma.cu) when they take the sizes -- the
+        decode form for steps of at most four tokens an entry (keys in slices, as many blocks as run at the
+        same time, added by a second kernel), the rows form for prompts, portions and mixed steps.  Else
+        float32 arithmetic: a bfloat16 decode step in key slices too; the float32 path always one block per
+        16 rows, whose sums do not depend on the batch."""
         if q.dtype != torch.float32:
             raise ShapeError("paged_attention_general: float32 queries")
         n = ctx.n_entries
-        decode = ctx.max_q_len * (nq // nkv) <= self.GENERAL_ROWS
-        if (k_cache.dtype == torch.bfloat16 and not decode and self.general_attention_on_tensor_cores
-                and self.lib.srlm_attention_general_mma_takes(C.c_int(dk), C.c_int(dv), C.c_int(int(v_cache is None)))):
+        g = nq // nkv
+        bf16 = k_cache.dtype == torch.bfloat16
+        tensor_cores = bf16 and self.general_attention_on_tensor_cores
+        from_keys = C.c_int(int(v_cache is None))
+        # a decode step: one to four tokens an entry.  Its keys are cut into slices, as many blocks as run at once.
+        if (tensor_cores and ctx.max_q_len <= 4 and not window
+                and self.lib.srlm_attention_general_decode_takes(C.c_int(dk), C.c_int(dv), from_keys)):
+            rows_padded = (ctx.max_q_len * g + 15) // 16 * 16
+            nsplit, chunk = self.attention_split(n, nkv * (rows_padded // 16), ctx.kv_bound, max_slices=64)
+            if not self.split_general_attention:
+                nsplit, chunk = 1, 0
+            part_o = part_ml = None
+            if nsplit > 1:
+                part_o = ctx.workspace.get("attn.general_part_o", n * nkv * nsplit * rows_padded, dv, torch.float32,
+                                           reserve=0)
+                part_ml = ctx.workspace.get("attn.general_part_ml", n * nkv * nsplit * rows_padded, 2, torch.float32,
+                                            reserve=0)
+            self._check(self.lib.srlm_paged_attention_general_decode(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), dtype_code(out.dtype), _ptr(block_table),
+                C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks), C.c_int(n),
+                C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv), C.c_int(k_cache.shape[2]),
+                C.c_float(scale), C.c_int(window or 0), C.c_int(nsplit), C.c_int(chunk), _ptr(part_o), _ptr(part_ml),
+                _stream()), "paged_attention_general_decode")
+            if nsplit > 1:
+                self._check(self.lib.srlm_attention_general_merge(
+                    _ptr(part_o), _ptr(part_ml), _ptr(out), dtype_code(out.dtype), _ptr(ctx.cu_q), C.c_int(n),
+                    C.c_int(nq), C.c_int(nkv), C.c_int(dv), C.c_int(nsplit), C.c_int(rows_padded), _stream()),
+                    "attention_general_merge")
+            return
+        decode = ctx.max_q_len * g <= self.GENERAL_ROWS
+        if (tensor_cores and not decode
+                and self.lib.srlm_attention_general_mma_takes(C.c_int(dk), C.c_int(dv), from_keys)):
             # prompts and their portions: bfloat16 tensor cores (the queries are rounded as they are loaded)
             self._check(self.lib.srlm_paged_attention_general_mma(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), dtype_code(out.dtype), _ptr(block_table),
@@ -782,9 +811,9 @@ class KernelLibrary:
                 C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), _stream()),
                 "paged_attention_general_mma")
             return
+        # float32, and sizes the tensor-core forms do not take: float32 arithmetic; a bfloat16 decode step in slices
         nsplit, chunk, part_o, part_ml = 1, 0, None, None
-        if (k_cache.dtype == torch.bfloat16 and ctx.max_q_len * (nq // nkv) <= self.GENERAL_ROWS and not window
-                and self.split_general_attention):
+        if bf16 and decode and not window and self.split_general_attention:
             nsplit, chunk = self.attention_split(n, nkv, ctx.kv_bound, max_slices=64)
             if nsplit > 1:
                 part_o = ctx.workspace.get("attn.general_part_o", n * nkv * nsplit * self.GENERAL_ROWS, dv,
