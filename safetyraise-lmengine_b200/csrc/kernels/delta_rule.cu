@@ -20,7 +20,7 @@ namespace srlm {
 
 constexpr int kMaxTaps = 8;
 constexpr int kLanesPerColumn = 8;       // lanes that share one column of S, each with every 8th row
-constexpr int kColumnsPerBlock = 32;
+constexpr int kColumnsPerBlock = 16;      // 16 x 8 lanes = 4 warps a block, one a scheduler: the recurrence is a chain
 
 template <typename TP>
 __global__ void delta_prepare_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ conv_w,
@@ -28,8 +28,9 @@ __global__ void delta_prepare_kernel(const TP* __restrict__ proj, long long ldp,
                                      const float* __restrict__ state, long long state_stride,
                                      const int* __restrict__ entry_of_token, const int* __restrict__ cu_q,
                                      const int* __restrict__ slots, float* __restrict__ qkv_out,
-                                     float* __restrict__ beta_out, float* __restrict__ decay_out, int H, int G, int dk,
-                                     int dv, int taps, float unit_eps) {
+                                     float* __restrict__ beta_out, float* __restrict__ decay_out,
+                                     float* __restrict__ qk_out, int H, int G, int dk, int dv, int taps,
+                                     float unit_eps) {
   extern __shared__ float ch[];                              // [C] convolved and activated channels of this token
   const int t = blockIdx.x;
   const int C = 2 * G * dk + H * dv;
@@ -59,6 +60,12 @@ __global__ void delta_prepare_kernel(const TP* __restrict__ proj, long long ldp,
     for (int d = lane; d < dk; d += 32) v[d] *= inv;
   }
   __syncthreads();
+  for (int hh = warp; hh < G; hh += nwarps) {                // q . k of each q / k head: the same for every column of S
+    float dot = 0.f;
+    for (int d = lane; d < dk; d += 32) dot += ch[(size_t)hh * dk + d] * ch[(size_t)(G + hh) * dk + d];
+    dot = warp_sum(dot);
+    if (lane == 0) qk_out[(size_t)t * G + hh] = dot;
+  }
   for (int c = threadIdx.x; c < C; c += blockDim.x) qkv_out[(size_t)t * C + c] = ch[c];
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     const float b = to_float(proj[(size_t)t * ldp + C + h]);
@@ -94,14 +101,14 @@ __global__ void delta_conv_carry_kernel(const TP* __restrict__ proj, long long l
   }
 }
 
-// Block: 32 columns of one head's S for one entry; a column is shared by 8 lanes, lane l holding rows
+// Block: 16 columns of one head's S for one entry; a column is shared by 8 lanes, lane l holding rows
 // 32 j + 4 l + {0..3} (RPL of them, four consecutive at a time so that shared memory is read 16 bytes a
 // lane).  The entry's tokens come through shared memory in chunks of 16, the next chunk fetched (cp.async)
 // while this one is worked on.  Per token the dependent chain is one round of partial sums over the OLD
 // state and one round of shuffles: with a = k . S and b = q . S (both over the state before the token)
-// and c = q . k,
+// and c = q . k (the same for every column: delta_prepare forms it),
 //     u = beta (v - g a),   S <- g S + k u,   o = g b + c u      ( = q . S after the write )
-// so the three sums are reduced side by side and the state update is one FMA deep.
+// so the two sums are reduced side by side and the state update is one FMA deep.
 constexpr int kChunk = 16;
 
 __device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
@@ -112,10 +119,10 @@ __device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
 template <int RPL>
 __global__ void __launch_bounds__(kColumnsPerBlock* kLanesPerColumn)
 delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
-                        float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
+                        const float* __restrict__ qk, float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ slots, float* __restrict__ o_out, int H, int G, int dk, int dv) {
   constexpr int DKP = RPL * kLanesPerColumn;                 // rows held in shared memory (zero beyond dk)
-  constexpr int ROW = 2 * DKP + kColumnsPerBlock + 4;        // k | q | v of the block's columns | beta, g, -, -
+  constexpr int ROW = 2 * DKP + kColumnsPerBlock + 4;        // k | q | v of the block's columns | beta, g, q.k, -
   extern __shared__ __align__(16) float stage[];            // [2][kChunk][ROW]
   const int e = blockIdx.z, h = blockIdx.y;
   const int cg = threadIdx.x / kLanesPerColumn, l = threadIdx.x % kLanesPerColumn;
@@ -151,6 +158,7 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       cp_async_4(st + i * ROW + 2 * DKP + kColumnsPerBlock, beta + (size_t)(t0 + base + i) * H + h);
       cp_async_4(st + i * ROW + 2 * DKP + kColumnsPerBlock + 1, decay + (size_t)(t0 + base + i) * H + h);
+      cp_async_4(st + i * ROW + 2 * DKP + kColumnsPerBlock + 2, qk + (size_t)(t0 + base + i) * G + kh);
     }
     asm volatile("cp.async.commit_group;" ::);
   };
@@ -178,20 +186,18 @@ delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__
         qq[4 * j] = qv.x; qq[4 * j + 1] = qv.y; qq[4 * j + 2] = qv.z; qq[4 * j + 3] = qv.w;
       }
       const float v = row[2 * DKP + cg], bt = row[2 * DKP + kColumnsPerBlock], g = row[2 * DKP + kColumnsPerBlock + 1];
-      float a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f}, c4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float cc = row[2 * DKP + kColumnsPerBlock + 2];
+      float a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int j = 0; j < RPL; ++j) {                        // four running sums each: no chain of RPL additions
         a4[j & 3] += kk[j] * S[j];
         b4[j & 3] += qq[j] * S[j];
-        c4[j & 3] += qq[j] * kk[j];
       }
       float a = (a4[0] + a4[1]) + (a4[2] + a4[3]), b = (b4[0] + b4[1]) + (b4[2] + b4[3]);
-      float cc = (c4[0] + c4[1]) + (c4[2] + c4[3]);
 #pragma unroll
       for (int off = 1; off < kLanesPerColumn; off <<= 1) {
         a += __shfl_xor_sync(0xffffffffu, a, off);
         b += __shfl_xor_sync(0xffffffffu, b, off);
-        cc += __shfl_xor_sync(0xffffffffu, cc, off);
       }
       const float u = bt * (v - g * a);
 #pragma unroll
@@ -238,8 +244,8 @@ static int delta_sizes_ok(int H, int G, int dk, int dv, int taps) {
 extern "C" int srlm_delta_prepare(const void* proj, int proj_dtype, long long ldp, const float* conv_w,
                                   const float* a_log, const float* dt_bias, float* state, long long state_stride,
                                   const int* entry_of_token, const int* cu_q, const int* slots, int n_entries,
-                                  float* qkv_out, float* beta_out, float* decay_out, int T, int H, int G, int dk,
-                                  int dv, int taps, float unit_eps, cudaStream_t stream) {
+                                  float* qkv_out, float* beta_out, float* decay_out, float* qk_out, int T, int H,
+                                  int G, int dk, int dv, int taps, float unit_eps, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   const long long C = 2LL * G * dk + (long long)H * dv;
   if (!delta_sizes_ok(H, G, dk, dv, taps) || ldp < C + 2LL * H + (long long)H * dv || C * 4 > 200 * 1024 ||
@@ -251,8 +257,8 @@ extern "C" int srlm_delta_prepare(const void* proj, int proj_dtype, long long ld
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(delta_prepare_kernel<TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     delta_prepare_kernel<TP><<<T, 256, smem, stream>>>((const TP*)proj, ldp, conv_w, a_log, dt_bias, state, state_stride,
-                                                       entry_of_token, cu_q, slots, qkv_out, beta_out, decay_out, H, G,
-                                                       dk, dv, taps, unit_eps);
+                                                       entry_of_token, cu_q, slots, qkv_out, beta_out, decay_out, qk_out,
+                                                       H, G, dk, dv, taps, unit_eps);
     if (taps > 1) {
       const long long n = (long long)n_entries * C;
       delta_conv_carry_kernel<TP><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
@@ -262,7 +268,7 @@ extern "C" int srlm_delta_prepare(const void* proj, int proj_dtype, long long ld
   return launched();
 }
 
-extern "C" int srlm_delta_recurrence(const float* qkv, const float* beta, const float* decay, float* state,
+extern "C" int srlm_delta_recurrence(const float* qkv, const float* beta, const float* decay, const float* qk, float* state,
                                      long long state_stride, const int* cu_q, const int* slots, int n_entries,
                                      float* o_out, int H, int G, int dk, int dv, cudaStream_t stream) {
   if (n_entries <= 0) return ST_OK;
@@ -276,7 +282,7 @@ extern "C" int srlm_delta_recurrence(const float* qkv, const float* beta, const 
     const size_t smem = (size_t)2 * kChunk * (2 * R * kLanesPerColumn + kColumnsPerBlock + 4) * sizeof(float);   \
     if (smem > 48 * 1024)                                                                                        \
       cudaFuncSetAttribute(delta_recurrence_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    delta_recurrence_kernel<R><<<grid, threads, smem, stream>>>(qkv, beta, decay, state, state_stride, cu_q,     \
+    delta_recurrence_kernel<R><<<grid, threads, smem, stream>>>(qkv, beta, decay, qk, state, state_stride, cu_q, \
                                                                 slots, o_out, H, G, dk, dv);                     \
   } while (0)
   if (rpl <= 4) SRLM_DELTA_CASE(4);

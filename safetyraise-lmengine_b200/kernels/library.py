@@ -869,22 +869,22 @@ class KernelLibrary:
             C.c_int(heads), C.c_int(rank), C.c_int(dv), _stream()), "latent_expand")
 
     # ---- the gated delta rule ------------------------------------------------------------------
-    def delta_prepare(self, ctx, proj, conv_w, a_log, dt_bias, state, qkv_out, beta_out, decay_out, H, G, dk, dv,
-                      taps, unit_eps):
+    def delta_prepare(self, ctx, proj, conv_w, a_log, dt_bias, state, qkv_out, beta_out, decay_out, qk_out, H, G, dk,
+                      dv, taps, unit_eps):
         """Convolution + SiLU of the q | k | v columns of proj (carrying each slot's last taps-1 inputs in its
-        state), unit vectors, beta and decay for every token; then the slots' carried inputs are renewed.
+        state), unit vectors, beta, decay and q . k (float32 [T, G]) for every token; then the slots' carried inputs are renewed.
         state: float32 [slots, state_size], laid out as csrc/kernels/delta_rule.cu says."""
         self._check(self.lib.srlm_delta_prepare(
             _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(conv_w), _ptr(a_log), _ptr(dt_bias),
             _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.entry_of_token), _ptr(ctx.cu_q), _ptr(ctx.slots),
-            C.c_int(ctx.n_entries), _ptr(qkv_out), _ptr(beta_out), _ptr(decay_out), C.c_int(proj.shape[0]), C.c_int(H),
-            C.c_int(G), C.c_int(dk), C.c_int(dv), C.c_int(taps), C.c_float(unit_eps), _stream()), "delta_prepare")
+            C.c_int(ctx.n_entries), _ptr(qkv_out), _ptr(beta_out), _ptr(decay_out), _ptr(qk_out), C.c_int(proj.shape[0]),
+            C.c_int(H), C.c_int(G), C.c_int(dk), C.c_int(dv), C.c_int(taps), C.c_float(unit_eps), _stream()), "delta_prepare")
         if taps > 1:
             self.launches += 1
 
-    def delta_recurrence(self, ctx, qkv, beta, decay, state, o_out, H, G, dk, dv):
+    def delta_recurrence(self, ctx, qkv, beta, decay, qk, state, o_out, H, G, dk, dv):
         self._check(self.lib.srlm_delta_recurrence(
-            _ptr(qkv), _ptr(beta), _ptr(decay), _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.cu_q),
+            _ptr(qkv), _ptr(beta), _ptr(decay), _ptr(qk), _ptr(state), C.c_longlong(state.stride(0)), _ptr(ctx.cu_q),
             _ptr(ctx.slots), C.c_int(ctx.n_entries), _ptr(o_out), C.c_int(H), C.c_int(G), C.c_int(dk), C.c_int(dv),
             _stream()), "delta_recurrence")
 

@@ -74,10 +74,11 @@ class DeltaRule(Part):
         qkv = ctx.workspace.get("delta.qkv", T, self.channels, torch.float32)
         beta = ctx.workspace.get("delta.beta", T, H, torch.float32)
         decay = ctx.workspace.get("delta.decay", T, H, torch.float32)
-        ops.delta_prepare(ctx, proj, self.conv_w, self.decay_log, self.decay_bias, state, qkv, beta, decay, H, G, dk,
-                          dv, s.conv_taps, s.unit_eps)
+        qk = ctx.workspace.get("delta.qk", T, G, torch.float32)
+        ops.delta_prepare(ctx, proj, self.conv_w, self.decay_log, self.decay_bias, state, qkv, beta, decay, qk, H, G,
+                          dk, dv, s.conv_taps, s.unit_eps)
         o = ctx.workspace.get("delta.o", T, H * dv, torch.float32)
-        ops.delta_recurrence(ctx, qkv, beta, decay, state, o, H, G, dk, dv)
+        ops.delta_recurrence(ctx, qkv, beta, decay, qk, state, o, H, G, dk, dv)
         gated = ctx.workspace.get("delta.out", T, H * dv, ctx.dtype)
         ops.delta_output(o, self.out_norm_w, s.norm_eps, proj, self.gate_off, gated, H, dv)
         return self.out(ctx, gated, "delta.proj_out")
