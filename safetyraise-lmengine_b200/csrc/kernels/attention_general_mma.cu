@@ -51,7 +51,13 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
                                    const int* __restrict__ block_table, int table_stride,
                                    const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                                    const float* __restrict__ sinks, int nq, int nkv, int dk, int dv, int page_size,
-                                   float scale, int window, int nbuf) {
+                                   float scale, int window, int nbuf, const bf16* __restrict__ kv_rows,
+                                   long long ld_rows, const int* __restrict__ cu_kv, int dim_rows, int v_off,
+                                   int page_skip) {
+  // kv_rows != null: every query head has keys and values of its own (nkv = nq), formed for this step in
+  // kv_rows, row cu_kv[e] + j for key j of entry e: the key's first dim_rows elements at column kvh * dim_rows,
+  // its values at column v_off + kvh * dv.  The key's other dk - dim_rows elements are shared by the heads and
+  // read from the pages (one KV head, rows of page_skip + dk - dim_rows elements, behind the first page_skip).
   constexpr int DVT = 8 * NT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int slabs = dv / DVT;
@@ -62,13 +68,14 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   const int r0 = blockIdx.x * kMmaRows;
   if (r0 >= rows) return;
   const int ks = dk + kPad;                                 // row strides in elements; rows stay 16-byte aligned
-  const int vs = v_cache ? DVT + kPad : ks;
+  const bool own_values = v_cache || kv_rows;               // a tile of values of their own, not the keys' leading part
+  const int vs = own_values ? DVT + kPad : ks;
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);            // [64][dk + 8]
   // nbuf = 2 when two tiles of keys (and values) fit beside the queries: the next tile is fetched (cp.async)
   // while this one is worked on; nbuf = 1: fetched, waited for, worked on
   bf16* k_s = q_s + kMmaRows * ks;                          // [nbuf][64][dk + 8]
-  bf16* v_s = v_cache ? k_s + nbuf * kMmaKeys * ks : k_s + slab * DVT;   // [nbuf][64][DVT + 8], or the slab's columns of the keys
-  const int k_tile = kMmaKeys * ks, v_tile = v_cache ? kMmaKeys * vs : k_tile;
+  bf16* v_s = own_values ? k_s + nbuf * kMmaKeys * ks : k_s + slab * DVT;   // [nbuf][64][DVT + 8], or the slab's columns of the keys
+  const int k_tile = kMmaKeys * ks, v_tile = own_values ? kMmaKeys * vs : k_tile;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int start = kv_len - q_len;
   const int* table = block_table + (size_t)e * table_stride;
@@ -103,19 +110,38 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   const int first_key = window > 0 ? max(0, min_pos - window + 1) : 0;
   const int kvec = dk / 8, vvec = DVT / 8;
 
+  const size_t row0 = kv_rows ? (size_t)cu_kv[e] : 0;
+  const int page_width = page_skip + dk - dim_rows;
   auto fetch = [&](int jb, int buf) {
     for (int idx = tid; idx < kMmaKeys * kvec; idx += blockDim.x) {
       const int jj = idx / kvec, c = idx - jj * kvec, j = jb + jj;
       const bool there = j <= max_pos;
-      const size_t rowi = there ? ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size) : 0;
-      cp_async_16(k_s + buf * k_tile + jj * ks + c * 8, k_cache + rowi * dk + c * 8, there);
+      const bf16* src = k_cache;
+      if (there && kv_rows) {
+        if (c * 8 < dim_rows) {
+          src = kv_rows + (row0 + j) * ld_rows + (size_t)kvh * dim_rows + c * 8;
+        } else {
+          const size_t rowi = (size_t)table[j / page_size] * page_size + (j % page_size);
+          src = k_cache + rowi * page_width + page_skip + (c * 8 - dim_rows);
+        }
+      } else if (there) {
+        const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
+        src = k_cache + rowi * dk + c * 8;
+      }
+      cp_async_16(k_s + buf * k_tile + jj * ks + c * 8, src, there);
     }
-    if (v_cache) {
+    if (v_cache || kv_rows) {
       for (int idx = tid; idx < kMmaKeys * vvec; idx += blockDim.x) {
         const int jj = idx / vvec, c = idx - jj * vvec, j = jb + jj;
         const bool there = j <= max_pos;
-        const size_t rowi = there ? ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size) : 0;
-        cp_async_16(v_s + buf * v_tile + jj * vs + c * 8, v_cache + rowi * dv + slab * DVT + c * 8, there);
+        const bf16* src = k_cache;
+        if (there && kv_rows) {
+          src = kv_rows + (row0 + j) * ld_rows + v_off + (size_t)kvh * dv + slab * DVT + c * 8;
+        } else if (there) {
+          const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
+          src = v_cache + rowi * dv + slab * DVT + c * 8;
+        }
+        cp_async_16(v_s + buf * v_tile + jj * vs + c * 8, src, there);
       }
     }
     cp_async_commit();
@@ -443,12 +469,13 @@ template <typename TO, int NT>
 static int launch_mma(dim3 grid, size_t smem, cudaStream_t stream, const float* q, const void* k_cache,
                       const void* v_cache, void* out, const int* block_table, int table_stride, const int* cu_q,
                       const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
-                      float scale, int window, int nbuf) {
+                      float scale, int window, int nbuf, const bf16* kv_rows = nullptr, long long ld_rows = 0,
+                      const int* cu_kv = nullptr, int dim_rows = 0, int v_off = 0, int page_skip = 0) {
   auto kern = paged_attention_general_mma_kernel<TO, NT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   kern<<<grid, kMmaWarps * 32, smem, stream>>>(q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out, block_table,
                                                table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale,
-                                               window, nbuf);
+                                               window, nbuf, kv_rows, ld_rows, cu_kv, dim_rows, v_off, page_skip);
   return launched();
 }
 
@@ -546,4 +573,40 @@ extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k
 #undef SRLM_DEC_SIZES
 #undef SRLM_DEC
   return launched();
+}
+
+// Prompts of an attention over a cached latent, in the heads' own space: q float32 [T, heads, dim + rot];
+// kv_rows bfloat16 [sum of the entries' contexts, ld_rows]: per row the heads' unrotated keys (heads x dim) and,
+// from column v_off, their values (heads x dv); pages: one KV head, rows [latent (rank) | rotated key part (rot)].
+extern "C" int srlm_latent_prefill_attention_takes(int dim, int rot, int dv, int rank) {
+  return dim > 0 && rot >= 0 && dim % 8 == 0 && rot % 8 == 0 && rank % 8 == 0 && (dim + rot) % 16 == 0 && dv % 64 == 0 &&
+         srlm_attention_general_mma_takes(dim + rot, dv, 0);
+}
+
+extern "C" int srlm_latent_prefill_attention(const float* q, const void* pages, const void* kv_rows, long long ld_rows,
+                                             const int* cu_kv, void* out, int out_dtype, const int* block_table,
+                                             int table_stride, const int* cu_q, const int* kv_lens, int n_entries,
+                                             int max_q_len, int heads, int dim, int rot, int dv, int rank, int v_off,
+                                             int page_size, float scale, cudaStream_t stream) {
+  if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  if (heads <= 0 || page_size <= 0 || !kv_rows || !cu_kv || !srlm_latent_prefill_attention_takes(dim, rot, dv, rank) ||
+      ld_rows % 8 || v_off % 8 || ld_rows < v_off + (long long)heads * dv)
+    return refuse(ST_BAD_SIZE, "latent_prefill_attention: heads=%d dim=%d rot=%d dv=%d rank=%d ld=%lld v_off=%d", heads, dim,
+                  rot, dv, rank, ld_rows, v_off);
+  if ((((uintptr_t)pages | (uintptr_t)kv_rows) & 15) != 0)
+    return refuse(ST_BAD_ALIGN, "latent_prefill_attention: pages and rows must be 16-byte aligned");
+  const int dk = dim + rot, slab = dv % 128 == 0 ? 128 : 64;
+  const long long tiles = ((long long)max_q_len + kMmaRows - 1) / kMmaRows, y = (long long)heads * (dv / slab);
+  if (n_entries > 65535 || y > 65535) return refuse(ST_BAD_SIZE, "latent_prefill_attention: %d entries", n_entries);
+  dim3 grid((unsigned)tiles, (unsigned)y, (unsigned)n_entries);
+  const size_t q_bytes = (size_t)kMmaRows * (dk + kPad) * 2;
+  const size_t tile_bytes = (size_t)kMmaKeys * (dk + kPad) * 2 + (size_t)kMmaKeys * (slab + kPad) * 2;
+  const int nbuf = q_bytes + 2 * tile_bytes <= 100 * 1024 ? 2 : 1;
+  const size_t smem = q_bytes + nbuf * tile_bytes;
+#define SRLM_LAT_ARGS grid, smem, stream, q, pages, nullptr, out, block_table, table_stride, cu_q, kv_lens, nullptr, heads, \
+                      heads, dk, dv, page_size, scale, 0, nbuf, (const bf16*)kv_rows, ld_rows, cu_kv, dim, v_off, rank
+  if (out_dtype == DT_F32) return slab == 128 ? launch_mma<float, 16>(SRLM_LAT_ARGS) : launch_mma<float, 8>(SRLM_LAT_ARGS);
+  if (out_dtype == DT_BF16) return slab == 128 ? launch_mma<bf16, 16>(SRLM_LAT_ARGS) : launch_mma<bf16, 8>(SRLM_LAT_ARGS);
+#undef SRLM_LAT_ARGS
+  return refuse(ST_BAD_DTYPE, "latent_prefill_attention: output dtype %d", out_dtype);
 }

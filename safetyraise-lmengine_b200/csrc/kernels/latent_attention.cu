@@ -118,6 +118,56 @@ __global__ void latent_expand_kernel(const float* __restrict__ o_lat, const TW* 
   }
 }
 
+// ---- prompts: per-head keys and values formed for the step ----------------------------------------------
+// A prompt attends in the heads' own space (dim + rot per key, vdim per value: a third of the latent form's
+// arithmetic).  latent_gather copies the latents of every entry's context out of the pages into one
+// contiguous matrix, row cu_kv[e] + j for key j of entry e; one matrix product with [U_k; U_v] then gives all
+// heads' unrotated keys and values; the rotated key part stays in the pages and is read from there.
+template <typename TC>
+__global__ void latent_gather_kernel(const TC* __restrict__ cache, TC* __restrict__ dst,
+                                     const int* __restrict__ block_table, int table_stride,
+                                     const int* __restrict__ cu_kv, int page_size, int width, int rank) {
+  const int e = blockIdx.y;
+  const int n = cu_kv[e + 1] - cu_kv[e];
+  const int* table = block_table + (size_t)e * table_stride;
+  for (int j = blockIdx.x; j < n; j += gridDim.x) {
+    const size_t row = (size_t)table[j / page_size] * page_size + (j % page_size);
+    TC* out = dst + (size_t)(cu_kv[e] + j) * rank;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) out[i] = cache[row * width + i];
+  }
+}
+
+// q_out float32 [T, heads, dim + rot]: the unrotated part as projected, the rest rotated.
+template <typename TP>
+__global__ void latent_rotate_q_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ cos_t,
+                                       const float* __restrict__ sin_t, int pairs, float* __restrict__ q_out,
+                                       int heads, int dim, int rot) {
+  const int t = blockIdx.x, hd = dim + rot;
+  for (int idx = threadIdx.x; idx < heads * hd; idx += blockDim.x) {
+    const int h = idx / hd, i = idx - h * hd;
+    const TP* src = proj + (size_t)t * ldp + (size_t)h * hd;
+    float v = to_float(src[i]);
+    const int r = i - dim;
+    if (r >= 0 && r < 2 * pairs) {
+      const float c = cos_t[(size_t)t * pairs + (r >> 1)], s = sin_t[(size_t)t * pairs + (r >> 1)];
+      const float other = to_float(src[dim + (r ^ 1)]);
+      v = (r & 1) ? v * c + other * s : v * c - other * s;
+    }
+    q_out[(size_t)t * heads * hd + idx] = v;
+  }
+}
+
+// out[t, h, :] = in[t, h, :] * sigmoid(proj[t, g_off + h])   (g_off < 0: no gate, a change of type only)
+template <typename TP, typename TA>
+__global__ void head_gate_kernel(const float* __restrict__ in, const TP* __restrict__ proj, long long ldp, int g_off,
+                                 TA* __restrict__ out, int heads, int dv) {
+  const int t = blockIdx.x;
+  for (int idx = threadIdx.x; idx < heads * dv; idx += blockDim.x) {
+    const float g = g_off >= 0 ? 1.f / (1.f + expf(-to_float(proj[(size_t)t * ldp + g_off + idx / dv]))) : 1.f;
+    out[(size_t)t * heads * dv + idx] = from_float<TA>(in[(size_t)t * heads * dv + idx] * g);
+  }
+}
+
 }  // namespace srlm
 
 using namespace srlm;
@@ -177,5 +227,43 @@ extern "C" int srlm_latent_expand(const float* o_lat, const void* uv_t, int w_dt
   else if (out_dtype == DT_BF16) SRLM_LATENT_TYPES(proj_dtype, w_dtype, SRLM_EXPAND(bf16));
   else return refuse(ST_BAD_DTYPE, "latent_expand: output dtype %d", out_dtype);
 #undef SRLM_EXPAND
+  return launched();
+}
+
+extern "C" int srlm_latent_gather(const void* cache, int cache_dtype, void* dst, const int* block_table, int table_stride,
+                                  const int* cu_kv, int n_entries, int max_kv_len, int page_size, int width, int rank,
+                                  cudaStream_t stream) {
+  if (n_entries <= 0 || max_kv_len <= 0) return ST_OK;
+  if (rank <= 0 || width < rank || page_size <= 0 || n_entries > 65535)
+    return refuse(ST_BAD_SIZE, "latent_gather: rank=%d width=%d page_size=%d entries=%d", rank, width, page_size, n_entries);
+  dim3 grid((unsigned)(max_kv_len < 4096 ? max_kv_len : 4096), (unsigned)n_entries);
+  SRLM_DISPATCH_ACT(cache_dtype, TC, (latent_gather_kernel<TC><<<grid, 64, 0, stream>>>(
+      (const TC*)cache, (TC*)dst, block_table, table_stride, cu_kv, page_size, width, rank)));
+  return launched();
+}
+
+extern "C" int srlm_latent_rotate_q(const void* proj, int proj_dtype, long long ldp, const float* cos_t,
+                                    const float* sin_t, int pairs, float* q_out, int T, int heads, int dim, int rot,
+                                    cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (heads <= 0 || dim <= 0 || rot < 0 || 2 * pairs > rot || ldp < (long long)heads * (dim + rot) ||
+      (pairs > 0 && (!cos_t || !sin_t)))
+    return refuse(ST_BAD_SIZE, "latent_rotate_q: heads=%d dim=%d rot=%d pairs=%d ldp=%lld", heads, dim, rot, pairs, ldp);
+  SRLM_DISPATCH_ACT(proj_dtype, TP, (latent_rotate_q_kernel<TP><<<T, 256, 0, stream>>>(
+      (const TP*)proj, ldp, cos_t, sin_t, pairs, q_out, heads, dim, rot)));
+  return launched();
+}
+
+extern "C" int srlm_head_gate(const float* in, const void* proj, int proj_dtype, long long ldp, int g_off, void* out,
+                              int out_dtype, int T, int heads, int dv, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (heads <= 0 || dv <= 0 || (g_off >= 0 && ldp < g_off + heads))
+    return refuse(ST_BAD_SIZE, "head_gate: heads=%d dv=%d g_off=%d ldp=%lld", heads, dv, g_off, ldp);
+#define SRLM_GATE(TP, TA) head_gate_kernel<TP, TA><<<T, 256, 0, stream>>>(in, (const TP*)proj, ldp, g_off, (TA*)out, heads, dv)
+  if (proj_dtype == DT_F32 && out_dtype == DT_F32) SRLM_GATE(float, float);
+  else if (proj_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_GATE(float, bf16);
+  else if (proj_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_GATE(bf16, bf16);
+  else return refuse(ST_BAD_DTYPE, "head_gate: projection dtype %d with output dtype %d", proj_dtype, out_dtype);
+#undef SRLM_GATE
   return launched();
 }

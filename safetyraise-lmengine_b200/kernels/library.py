@@ -72,6 +72,7 @@ class KernelLibrary:
         self.early_launch = True                # weight-streaming products may start under the kernel ahead of them
         self.split_general_attention = True     # decode steps of the general attention: the keys in slices
         self.general_attention_on_tensor_cores = True   # its prompts and portions: mma.sync, when the sizes fit
+        self.latent_prompts_in_head_space = True        # latent attention: prompts form per-head keys and values
 
     @property
     def lib(self):
@@ -867,6 +868,43 @@ class KernelLibrary:
             _ptr(o_lat), _ptr(uv_t), dtype_code(uv_t.dtype), _ptr(proj), dtype_code(proj.dtype),
             C.c_longlong(proj.stride(0)), C.c_int(g_off), _ptr(out), dtype_code(out.dtype), C.c_int(o_lat.shape[0]),
             C.c_int(heads), C.c_int(rank), C.c_int(dv), _stream()), "latent_expand")
+
+    def latent_prompt_takes(self, dim, rot, dv, rank) -> bool:
+        """Whether prompts of a latent attention of these sizes may attend in the heads' own space on tensor cores."""
+        return bool(self.latent_prompts_in_head_space and self.general_attention_on_tensor_cores
+                    and self.lib.srlm_latent_prefill_attention_takes(C.c_int(dim), C.c_int(rot), C.c_int(dv), C.c_int(rank)))
+
+    def latent_gather(self, ctx, cache, dst, block_table, cu_kv, rank):
+        """dst[cu_kv[e] + j] = the latent (first ``rank`` elements of the page row) of key j of entry e."""
+        self._check(self.lib.srlm_latent_gather(
+            _ptr(cache), dtype_code(cache.dtype), _ptr(dst), _ptr(block_table), C.c_int(block_table.stride(0)),
+            _ptr(cu_kv), C.c_int(ctx.n_entries), C.c_int(ctx.max_kv_len), C.c_int(cache.shape[2]),
+            C.c_int(cache.shape[3]), C.c_int(rank), _stream()), "latent_gather")
+
+    def latent_rotate_q(self, proj, rotation, q_out, heads, dim, rot):
+        pairs = rotation.pairs if rotation is not None else 0
+        self._check(self.lib.srlm_latent_rotate_q(
+            _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(rotation.cos if pairs else None),
+            _ptr(rotation.sin if pairs else None), C.c_int(pairs), _ptr(q_out), C.c_int(proj.shape[0]), C.c_int(heads),
+            C.c_int(dim), C.c_int(rot), _stream()), "latent_rotate_q")
+
+    def latent_prefill_attention(self, ctx, q, pages, kv_rows, cu_kv, out, block_table, heads, dim, rot, dv, rank,
+                                 v_off, scale):
+        """Causal attention of prompts in the heads' own space: q float32 [T, heads * (dim + rot)]; kv_rows bfloat16
+        [keys of all entries, >= v_off + heads * dv] with the heads' unrotated keys and, from column v_off, values;
+        the rotated key part comes from the pages."""
+        self._check(self.lib.srlm_latent_prefill_attention(
+            _ptr(q), _ptr(pages), _ptr(kv_rows), C.c_longlong(kv_rows.stride(0)), _ptr(cu_kv), _ptr(out),
+            dtype_code(out.dtype), _ptr(block_table), C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens),
+            C.c_int(ctx.n_entries), C.c_int(ctx.max_q_len), C.c_int(heads), C.c_int(dim), C.c_int(rot), C.c_int(dv),
+            C.c_int(rank), C.c_int(v_off), C.c_int(pages.shape[2]), C.c_float(scale), _stream()),
+            "latent_prefill_attention")
+
+    def head_gate(self, x, proj, g_off, out, heads, dv):
+        """out[t, h, :] = x[t, h, :] * sigmoid(proj[t, g_off + h]); x float32; g_off < 0: no gate."""
+        self._check(self.lib.srlm_head_gate(
+            _ptr(x), _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), C.c_int(g_off), _ptr(out),
+            dtype_code(out.dtype), C.c_int(x.shape[0]), C.c_int(heads), C.c_int(dv), _stream()), "head_gate")
 
     # ---- the gated delta rule ------------------------------------------------------------------
     def delta_prepare(self, ctx, proj, conv_w, a_log, dt_bias, state, qkv_out, beta_out, decay_out, qk_out, H, G, dk,

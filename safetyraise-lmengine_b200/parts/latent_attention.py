@@ -5,9 +5,16 @@ rotated key part (rot_dim elements) that all heads share.  Head h's unrotated ke
 value U_v,h c; the score of query i on key j is (q_i . U_k,h c_j + qr_i . kr_j) * scale.  Neither keys
 nor values are formed: the up projection of the keys is folded into the query (U_k,h^T q_i), the
 attention runs over [c | kr] with the values being c itself, and the up projection of the values is
-applied to the attended latent.  The result does not depend on how a prompt is cut: every step runs
-the same three kernels around the same attention kernel.  Each head's output is multiplied by the
-sigmoid of a projection of the mixer's input before the output projection.
+applied to the attended latent.  Each head's output is multiplied by the sigmoid of a projection of
+the mixer's input before the output projection.
+
+Prompts in bfloat16 (steps with an entry of more than four tokens) take the other road when the sizes
+fit the tensor-core kernel: the latents of the entries' whole contexts are gathered from the pages, one
+matrix product with [U_k; U_v] forms every head's unrotated keys and values for this step only, and the
+attention runs in the heads' own space (dim + rot_dim per key, vdim per value: a third of the latent
+form's arithmetic); the rotated key part is read from the pages.  What the pages hold is the same on
+both roads, so a request may change between them from step to step; the float32 path always attends
+in the latent space and its logits do not depend on the cutting.
 """
 from __future__ import annotations
 
@@ -38,6 +45,10 @@ class LatentAttention(Part):
         # per head [kv_rank, v_head_dim]: a thread of the expanding kernel owns one output column
         self.uv_t = tensors[p + nm.up_v].view(s.heads, s.v_head_dim, s.kv_rank).transpose(1, 2).contiguous()
         self.out = Linear(tensors[p + nm.o], p + nm.o)
+        # [U_k; U_v] as one weight, for prompts that form per-head keys and values (bfloat16 only)
+        self.up_kv = None
+        if mctx.dtype == torch.bfloat16 and tensors[p + nm.up_k].dtype == torch.bfloat16:
+            self.up_kv = torch.cat([tensors[p + nm.up_k], tensors[p + nm.up_v]], dim=0).contiguous()
         self.position = None
         if s.position is not None:
             self.position = lookup(POSITION_ENCODINGS, s.position.kind, "position encoding")(s.position, mctx)
@@ -73,12 +84,41 @@ class LatentAttention(Part):
         if run_step.writes_cache:
             ops.latent_append(proj, self.c_off, self.latent_norm_w, s.latent_norm_eps, rot, cache, ctx.kv_slot[group],
                               s.kv_rank, s.rot_dim)
+        gated = ctx.workspace.get("latent.out", T, s.heads * s.v_head_dim, ctx.dtype)
+        if (self.up_kv is not None and ctx.max_q_len > 4 and run_step.writes_cache
+                and ops.latent_prompt_takes(s.head_dim, s.rot_dim, s.v_head_dim, s.kv_rank)):
+            self._attend_in_head_space(ctx, proj, cache, group, rot, gated)
+            return self.out(ctx, gated, "latent.proj_out")
         qd = s.kv_rank + s.rot_dim
         q = ctx.workspace.get("latent.q", T, s.heads * qd, torch.float32)
         ops.latent_absorb(proj, self.uk, rot, q, s.heads, s.head_dim, s.rot_dim, s.kv_rank)
         o_lat = ctx.workspace.get("latent.o", T, s.heads * s.kv_rank, torch.float32)
         ops.paged_attention_general(ctx, q, cache, None, o_lat, ctx.block_tables[group], None, s.heads, 1, qd,
                                     s.kv_rank, s.softmax_scale)
-        gated = ctx.workspace.get("latent.out", T, s.heads * s.v_head_dim, ctx.dtype)
         ops.latent_expand(o_lat, self.uv_t, proj, self.g_off, gated, s.heads, s.kv_rank, s.v_head_dim)
         return self.out(ctx, gated, "latent.proj_out")
+
+    def _attend_in_head_space(self, ctx, proj, cache, group, rot, gated) -> None:
+        """Prompts: gather the contexts' latents, form all heads' unrotated keys and values with one product,
+        attend per head, gate.  The row of key j of entry e in the gathered matrices is cu_kv[e] + j."""
+        s = self.spec
+        T = proj.shape[0]
+        cu_kv = ctx.tables.get("latent.cu_kv")
+        if cu_kv is None:
+            sums = [0]
+            for n in ctx.host["kv_lens"]:
+                sums.append(sums[-1] + n)
+            cu_kv = ctx.tables["latent.cu_kv"] = torch.tensor(sums, dtype=torch.int32).pin_memory().to(
+                proj.device, non_blocking=True)
+            ctx.tables["latent.keys"] = sums[-1]
+        keys = ctx.tables["latent.keys"]
+        latents = ctx.workspace.get("latent.gathered", keys, s.kv_rank, ctx.dtype)
+        ops.latent_gather(ctx, cache, latents, ctx.block_tables[group], cu_kv, s.kv_rank)
+        kv_rows = ctx.workspace.get("latent.kv_rows", keys, s.heads * (s.head_dim + s.v_head_dim), ctx.dtype)
+        ops.gemm(latents, self.up_kv, kv_rows)
+        q = ctx.workspace.get("latent.q_heads", T, s.heads * (s.head_dim + s.rot_dim), torch.float32)
+        ops.latent_rotate_q(proj, rot, q, s.heads, s.head_dim, s.rot_dim)
+        attended = ctx.workspace.get("latent.o_heads", T, s.heads * s.v_head_dim, torch.float32)
+        ops.latent_prefill_attention(ctx, q, cache, kv_rows, cu_kv, attended, ctx.block_tables[group], s.heads,
+                                     s.head_dim, s.rot_dim, s.v_head_dim, s.kv_rank, s.heads * s.head_dim, s.softmax_scale)
+        ops.head_gate(attended, proj, self.g_off, gated, s.heads, s.v_head_dim)
