@@ -238,7 +238,7 @@ __global__ void delta_output_kernel(const float* __restrict__ o, const float* __
 using namespace srlm;
 
 static int delta_sizes_ok(int H, int G, int dk, int dv, int taps) {
-  return H > 0 && G > 0 && H % G == 0 && dk > 0 && dk <= 256 && dv > 0 && taps >= 1 && taps <= kMaxTaps;
+  return H > 0 && G > 0 && H % G == 0 && dk > 0 && dk <= 512 && dv > 0 && taps >= 1 && taps <= kMaxTaps;
 }
 
 extern "C" int srlm_delta_prepare(const void* proj, int proj_dtype, long long ldp, const float* conv_w,
@@ -250,7 +250,7 @@ extern "C" int srlm_delta_prepare(const void* proj, int proj_dtype, long long ld
   const long long C = 2LL * G * dk + (long long)H * dv;
   if (!delta_sizes_ok(H, G, dk, dv, taps) || ldp < C + 2LL * H + (long long)H * dv || C * 4 > 200 * 1024 ||
       state_stride < (long long)H * dk * dv + C * (taps - 1))
-    return refuse(ST_BAD_SIZE, "delta_prepare: H=%d G=%d dk=%d dv=%d taps=%d ldp=%lld state=%lld (dk <= 256, taps <= %d)",
+    return refuse(ST_BAD_SIZE, "delta_prepare: H=%d G=%d dk=%d dv=%d taps=%d ldp=%lld state=%lld (dk <= 512, taps <= %d)",
                   H, G, dk, dv, taps, ldp, state_stride, kMaxTaps);
   const size_t smem = (size_t)C * sizeof(float);
   SRLM_DISPATCH_ACT(proj_dtype, TP, {
@@ -273,7 +273,7 @@ extern "C" int srlm_delta_recurrence(const float* qkv, const float* beta, const 
                                      float* o_out, int H, int G, int dk, int dv, cudaStream_t stream) {
   if (n_entries <= 0) return ST_OK;
   if (!delta_sizes_ok(H, G, dk, dv, 1) || n_entries > 65535 || H > 65535)
-    return refuse(ST_BAD_SIZE, "delta_recurrence: H=%d G=%d dk=%d dv=%d entries=%d (dk <= 256)", H, G, dk, dv, n_entries);
+    return refuse(ST_BAD_SIZE, "delta_recurrence: H=%d G=%d dk=%d dv=%d entries=%d (dk <= 512)", H, G, dk, dv, n_entries);
   dim3 grid((dv + kColumnsPerBlock - 1) / kColumnsPerBlock, H, n_entries);
   const int threads = kColumnsPerBlock * kLanesPerColumn;
   const int rpl = (dk + kLanesPerColumn - 1) / kLanesPerColumn;
@@ -288,7 +288,8 @@ extern "C" int srlm_delta_recurrence(const float* qkv, const float* beta, const 
   if (rpl <= 4) SRLM_DELTA_CASE(4);
   else if (rpl <= 8) SRLM_DELTA_CASE(8);
   else if (rpl <= 16) SRLM_DELTA_CASE(16);
-  else SRLM_DELTA_CASE(32);
+  else if (rpl <= 32) SRLM_DELTA_CASE(32);
+  else SRLM_DELTA_CASE(64);     // heads of up to 512: the state no longer fits the registers, and runs from local memory
 #undef SRLM_DELTA_CASE
   return launched();
 }

@@ -46,13 +46,50 @@ __global__ void latent_append_kernel(const TP* __restrict__ proj, long long ldp,
   }
 }
 
-// Block (token tile, head).  q row: heads x [dim unrotated | rot rotated].  uk: [heads, dim, rank].
-// q_out: float32 [T, heads, rank + rot].
+// The two per-head products: out[t, h, c] = sum_k in[t, h, k] * W[h, k, c].  A block takes 16 tokens, one head
+// and 32 columns; its four warps each take a quarter of k (a lane owns a column, so a warp reads 32
+// consecutive weights) and their partial sums are added in warp order through shared memory: the order of
+// every sum depends on the sizes alone.  Decode steps launch heads x columns / 32 blocks, not one per head.
+constexpr int kColTile = 32, kProductWarps = 4;
+
+template <typename TW>
+__device__ __forceinline__ void head_product(const float* __restrict__ in_s, int K, const TW* __restrict__ w, int cols,
+                                             int col, float* __restrict__ red, float (&sum)[kTokTile / kProductWarps]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int per = (K + kProductWarps - 1) / kProductWarps, k0 = warp * per, k1 = min(K, k0 + per);
+  float acc[kTokTile];
+#pragma unroll
+  for (int tt = 0; tt < kTokTile; ++tt) acc[tt] = 0.f;
+  if (col < cols) {
+    for (int k = k0; k < k1; ++k) {
+      const float wv = to_float(w[(size_t)k * cols + col]);
+#pragma unroll
+      for (int tt = 0; tt < kTokTile; ++tt) acc[tt] += in_s[tt * K + k] * wv;
+    }
+  }
+#pragma unroll
+  for (int tt = 0; tt < kTokTile; ++tt) red[(warp * kTokTile + tt) * kColTile + lane] = acc[tt];
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kTokTile / kProductWarps; ++i) {      // this warp finishes four of the sixteen tokens
+    const int tt = warp * (kTokTile / kProductWarps) + i;
+    float v = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < kProductWarps; ++ww) v += red[(ww * kTokTile + tt) * kColTile + lane];
+    sum[i] = v;
+  }
+}
+
+// Block (token tile, head, 32 columns of the latent).  q row: heads x [dim unrotated | rot rotated].
+// uk: [heads, dim, rank].  q_out: float32 [T, heads, rank + rot]; the blocks of the first columns also rotate.
 template <typename TP, typename TW>
-__global__ void latent_absorb_kernel(const TP* __restrict__ proj, long long ldp, const TW* __restrict__ uk,
-                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairs,
-                                     float* __restrict__ q_out, int T, int heads, int dim, int rot, int rank) {
-  extern __shared__ float q_s[];                             // [kTokTile][dim]
+__global__ void __launch_bounds__(kProductWarps * 32)
+latent_absorb_kernel(const TP* __restrict__ proj, long long ldp, const TW* __restrict__ uk,
+                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairs,
+                     float* __restrict__ q_out, int T, int heads, int dim, int rot, int rank) {
+  extern __shared__ float sh[];                              // [kTokTile][dim] | [warps][kTokTile][32]
+  float* q_s = sh;
+  float* red = sh + kTokTile * dim;
   const int t0 = blockIdx.x * kTokTile, h = blockIdx.y;
   const int n = min(kTokTile, T - t0);
   for (int idx = threadIdx.x; idx < kTokTile * dim; idx += blockDim.x) {
@@ -60,19 +97,16 @@ __global__ void latent_absorb_kernel(const TP* __restrict__ proj, long long ldp,
     q_s[idx] = tt < n ? to_float(proj[(size_t)(t0 + tt) * ldp + (size_t)h * (dim + rot) + d]) : 0.f;
   }
   __syncthreads();
-  const int qd = rank + rot;
-  const TW* w = uk + (size_t)h * dim * rank;
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) {
-    float acc[kTokTile];
+  const int qd = rank + rot, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.z * kColTile + lane;
+  float sum[kTokTile / kProductWarps];
+  head_product(q_s, dim, uk + (size_t)h * dim * rank, rank, col, red, sum);
 #pragma unroll
-    for (int tt = 0; tt < kTokTile; ++tt) acc[tt] = 0.f;
-    for (int d = 0; d < dim; ++d) {
-      const float wv = to_float(w[(size_t)d * rank + r]);
-#pragma unroll
-      for (int tt = 0; tt < kTokTile; ++tt) acc[tt] += q_s[tt * dim + d] * wv;
-    }
-    for (int tt = 0; tt < n; ++tt) q_out[((size_t)(t0 + tt) * heads + h) * qd + r] = acc[tt];
+  for (int i = 0; i < kTokTile / kProductWarps; ++i) {
+    const int tt = warp * (kTokTile / kProductWarps) + i;
+    if (tt < n && col < rank) q_out[((size_t)(t0 + tt) * heads + h) * qd + col] = sum[i];
   }
+  if (blockIdx.z != 0) return;
   for (int idx = threadIdx.x; idx < n * rot; idx += blockDim.x) {
     const int tt = idx / rot, i = idx - tt * rot, t = t0 + tt;
     const TP* src = proj + (size_t)t * ldp + (size_t)h * (dim + rot) + dim;
@@ -86,13 +120,15 @@ __global__ void latent_absorb_kernel(const TP* __restrict__ proj, long long ldp,
   }
 }
 
-// Block (token tile, head).  o_lat: float32 [T, heads, rank]; uv_t: [heads, rank, dv] (the up projection
-// of the values, transposed per head); gate: column g_off + h of the projection row, or none.
+// Block (token tile, head, 32 value columns).  o_lat: float32 [T, heads, rank]; uv_t: [heads, rank, dv] (the up
+// projection of the values, transposed per head); gate: column g_off + h of the projection row, or none.
 template <typename TP, typename TW, typename TA>
-__global__ void latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ uv_t,
-                                     const TP* __restrict__ proj, long long ldp, int g_off, TA* __restrict__ out,
-                                     int T, int heads, int rank, int dv) {
-  extern __shared__ float o_s[];                             // [kTokTile][rank]
+__global__ void __launch_bounds__(kProductWarps * 32)
+latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ uv_t, const TP* __restrict__ proj,
+                     long long ldp, int g_off, TA* __restrict__ out, int T, int heads, int rank, int dv) {
+  extern __shared__ float sh[];                              // [kTokTile][rank] | [warps][kTokTile][32]
+  float* o_s = sh;
+  float* red = sh + kTokTile * rank;
   const int t0 = blockIdx.x * kTokTile, h = blockIdx.y;
   const int n = min(kTokTile, T - t0);
   for (int idx = threadIdx.x; idx < kTokTile * rank; idx += blockDim.x) {
@@ -100,21 +136,17 @@ __global__ void latent_expand_kernel(const float* __restrict__ o_lat, const TW* 
     o_s[idx] = tt < n ? o_lat[((size_t)(t0 + tt) * heads + h) * rank + r] : 0.f;
   }
   __syncthreads();
-  const TW* w = uv_t + (size_t)h * rank * dv;
-  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
-    float acc[kTokTile];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.z * kColTile + lane;
+  float sum[kTokTile / kProductWarps];
+  head_product(o_s, rank, uv_t + (size_t)h * rank * dv, dv, col, red, sum);
 #pragma unroll
-    for (int tt = 0; tt < kTokTile; ++tt) acc[tt] = 0.f;
-    for (int r = 0; r < rank; ++r) {
-      const float wv = to_float(w[(size_t)r * dv + j]);
-#pragma unroll
-      for (int tt = 0; tt < kTokTile; ++tt) acc[tt] += o_s[tt * rank + r] * wv;
-    }
-    for (int tt = 0; tt < n; ++tt) {
-      float g = 1.f;
-      if (g_off >= 0) g = 1.f / (1.f + expf(-to_float(proj[(size_t)(t0 + tt) * ldp + g_off + h])));
-      out[((size_t)(t0 + tt) * heads + h) * dv + j] = from_float<TA>(acc[tt] * g);
-    }
+  for (int i = 0; i < kTokTile / kProductWarps; ++i) {
+    const int tt = warp * (kTokTile / kProductWarps) + i;
+    if (tt >= n || col >= dv) continue;
+    float g = 1.f;
+    if (g_off >= 0) g = 1.f / (1.f + expf(-to_float(proj[(size_t)(t0 + tt) * ldp + g_off + h])));
+    out[((size_t)(t0 + tt) * heads + h) * dv + col] = from_float<TA>(sum[i] * g);
   }
 }
 
@@ -197,13 +229,13 @@ extern "C" int srlm_latent_absorb(const void* proj, int proj_dtype, long long ld
                                   const float* cos_t, const float* sin_t, int pairs, float* q_out, int T, int heads,
                                   int dim, int rot, int rank, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
-  const size_t smem = (size_t)kTokTile * dim * sizeof(float);
+  const size_t smem = ((size_t)kTokTile * dim + (size_t)kProductWarps * kTokTile * kColTile) * sizeof(float);
   if (heads <= 0 || heads > 65535 || dim <= 0 || rank <= 0 || rot < 0 || 2 * pairs > rot || smem > 48 * 1024 ||
       ldp < (long long)heads * (dim + rot) || (pairs > 0 && (!cos_t || !sin_t)))
     return refuse(ST_BAD_SIZE, "latent_absorb: heads=%d dim=%d rot=%d rank=%d pairs=%d ldp=%lld", heads, dim, rot, rank,
                   pairs, ldp);
-  dim3 grid((T + kTokTile - 1) / kTokTile, heads);
-  SRLM_LATENT_TYPES(proj_dtype, w_dtype, (latent_absorb_kernel<TP, TW><<<grid, 128, smem, stream>>>(
+  dim3 grid((T + kTokTile - 1) / kTokTile, heads, (rank + kColTile - 1) / kColTile);
+  SRLM_LATENT_TYPES(proj_dtype, w_dtype, (latent_absorb_kernel<TP, TW><<<grid, kProductWarps * 32, smem, stream>>>(
       (const TP*)proj, ldp, (const TW*)uk, cos_t, sin_t, pairs, q_out, T, heads, dim, rot, rank)));
   return launched();
 }
@@ -212,15 +244,15 @@ extern "C" int srlm_latent_expand(const float* o_lat, const void* uv_t, int w_dt
                                   long long ldp, int g_off, void* out, int out_dtype, int T, int heads, int rank,
                                   int dv, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
-  const size_t smem = (size_t)kTokTile * rank * sizeof(float);
+  const size_t smem = ((size_t)kTokTile * rank + (size_t)kProductWarps * kTokTile * kColTile) * sizeof(float);
   if (heads <= 0 || heads > 65535 || rank <= 0 || dv <= 0 || smem > 200 * 1024 || (g_off >= 0 && ldp < g_off + heads))
     return refuse(ST_BAD_SIZE, "latent_expand: heads=%d rank=%d dv=%d g_off=%d ldp=%lld", heads, rank, dv, g_off, ldp);
-  dim3 grid((T + kTokTile - 1) / kTokTile, heads);
+  dim3 grid((T + kTokTile - 1) / kTokTile, heads, (dv + kColTile - 1) / kColTile);
 #define SRLM_EXPAND(TA)                                                                                          \
   do {                                                                                                           \
     auto kern = latent_expand_kernel<TP, TW, TA>;                                                                \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    kern<<<grid, 128, smem, stream>>>(o_lat, (const TW*)uv_t, (const TP*)proj, ldp, g_off, (TA*)out, T, heads,   \
+    kern<<<grid, kProductWarps * 32, smem, stream>>>(o_lat, (const TW*)uv_t, (const TP*)proj, ldp, g_off, (TA*)out, T, heads,   \
                                       rank, dv);                                                                 \
   } while (0)
   if (out_dtype == DT_F32) SRLM_LATENT_TYPES(proj_dtype, w_dtype, SRLM_EXPAND(float));

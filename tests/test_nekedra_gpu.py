@@ -50,7 +50,8 @@ CONFIGS = {
                      delta(heads=2, kv_heads=2, dim=8, vdim=40, conv=2, ff=0), attention()]),
     # sizes that the tensor-core form of the attention takes (keys a multiple of 16, values of 64 or 128)
     "wide": config([attention(heads=4, kv_heads=2, dim=32, vdim=64), latent(heads=4, dim=16, rot_dim=16, dims=16, rank=128, vdim=64),
-                    attention(heads=4, kv_heads=2, dim=32, vdim=64), latent(heads=2, dim=32, rot_dim=16, dims=8, rank=64, vdim=16)],
+                    attention(heads=4, kv_heads=2, dim=32, vdim=64), latent(heads=2, dim=32, rot_dim=16, dims=8, rank=64, vdim=16),
+                    delta(heads=2, kv_heads=1, dim=272, vdim=16, conv=2)],       # a state too wide for a lane's registers
                    width=128, vocab=260),
     # sizes that are 1, odd or no multiple of 8: a width that the tensor-core products do not take
     "odd": config([delta(heads=1, kv_heads=1, dim=40, vdim=33, conv=1), latent(heads=1, dim=12, rot_dim=6, dims=2, rank=20, vdim=9),
