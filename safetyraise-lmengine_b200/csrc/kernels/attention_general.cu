@@ -30,6 +30,8 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
                                const int* __restrict__ kv_lens, const float* __restrict__ sinks, int nq, int nkv,
                                int dk, int dv, int page_size, float scale, int window, int nsplit, int kv_chunk,
                                float* __restrict__ part_o, float* __restrict__ part_ml) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   extern __shared__ float smem[];
   const int e = blockIdx.z, kvh = blockIdx.y;
   const int G = nq / nkv;
@@ -183,6 +185,8 @@ template <typename TO>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        TO* __restrict__ out, const int* __restrict__ cu_q, int n_entries, int nq,
                                        int nkv, int dv, int nsplit, int rows_padded) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   __shared__ float w[kMaxSlices];
   __shared__ float inv_l;
   const long long b = blockIdx.x;
@@ -224,6 +228,8 @@ __global__ void attention_bias_append_kernel(const TP* __restrict__ proj, long l
                                              float* __restrict__ v_keep, const float* __restrict__ lambda,
                                              int mix_mode, int write_kv, int nq, int nkv, int dk, int dv,
                                              int page_size) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   const int t = blockIdx.x;
   const TP* p = proj + (size_t)t * ldp;
   const int nqd = nq * dk, nkd = nkv * dk, nvd = nkv * dv;
@@ -258,7 +264,7 @@ static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, 
   case V: {                                                                                                    \
     auto kern = paged_attention_general_kernel<TC, TO, V>;                                                     \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    kern<<<grid, kWarps * 32, smem, stream>>>(q, (const TC*)k_cache, (const TC*)v_cache, (TO*)out, block_table, \
+    launch_pdl(kern, dim3(grid), dim3(kWarps * 32), smem, stream, q, (const TC*)k_cache, (const TC*)v_cache, (TO*)out, block_table, \
                                               table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size,  \
                                               scale, window, nsplit, kv_chunk, part_o, part_ml);               \
     break;                                                                                                     \
@@ -273,7 +279,7 @@ static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, 
 #undef SRLM_GENERAL_CASE
   if (nsplit > 1) {
     const long long blocks = (long long)n_entries * nkv * kRows;
-    attention_merge_kernel<TO><<<(unsigned)blocks, 128, 0, stream>>>(part_o, part_ml, (TO*)out, cu_q, n_entries, nq,
+    launch_pdl(attention_merge_kernel<TO>, dim3((unsigned)blocks), dim3(128), 0, stream, part_o, part_ml, (TO*)out, cu_q, n_entries, nq,
                                                                      nkv, dv, nsplit, kRows);
   }
   return launched();
@@ -337,7 +343,7 @@ extern "C" int srlm_attention_bias_append(const void* proj, int proj_dtype, long
     return refuse(ST_BAD_SIZE, "attention_bias_append: nq=%d nkv=%d dk=%d dv=%d ldp=%lld mix_mode=%d", nq, nkv, dk, dv,
                   ldp, mix_mode);
 #define SRLM_APPEND(TP, TC)                                                                                       \
-  attention_bias_append_kernel<TP, TC><<<T, 256, 0, stream>>>((const TP*)proj, ldp, bias, q_out, (TC*)k_cache,    \
+  launch_pdl(attention_bias_append_kernel<TP, TC>, dim3(T), dim3(256), 0, stream, (const TP*)proj, ldp, bias, q_out, (TC*)k_cache,    \
                                                               (TC*)v_cache, kv_slot, v_keep, lambda, mix_mode,   \
                                                               write_kv, nq, nkv, dk, dv, page_size)
   if (proj_dtype == DT_F32 && cache_dtype == DT_F32) SRLM_APPEND(float, float);
@@ -357,10 +363,10 @@ extern "C" int srlm_attention_general_merge(const float* part_o, const float* pa
     return refuse(ST_BAD_SIZE, "attention_general_merge: %d slices (at most %d), %d rows", nsplit, kMaxSlices, rows_padded);
   const long long blocks = (long long)n_entries * nkv * rows_padded;
   if (out_dtype == DT_F32)
-    attention_merge_kernel<float><<<(unsigned)blocks, 128, 0, stream>>>(part_o, part_ml, (float*)out, cu_q, n_entries, nq,
+    launch_pdl(attention_merge_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, stream, part_o, part_ml, (float*)out, cu_q, n_entries, nq,
                                                                         nkv, dv, nsplit, rows_padded);
   else if (out_dtype == DT_BF16)
-    attention_merge_kernel<bf16><<<(unsigned)blocks, 128, 0, stream>>>(part_o, part_ml, (bf16*)out, cu_q, n_entries, nq,
+    launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, stream, part_o, part_ml, (bf16*)out, cu_q, n_entries, nq,
                                                                        nkv, dv, nsplit, rows_padded);
   else
     return refuse(ST_BAD_DTYPE, "attention_general_merge: output dtype %d", out_dtype);

@@ -54,6 +54,8 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
                                    float scale, int window, int nbuf, const bf16* __restrict__ kv_rows,
                                    long long ld_rows, const int* __restrict__ cu_kv, int dim_rows, int v_off,
                                    int page_skip) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   // kv_rows != null: every query head has keys and values of its own (nkv = nq), formed for this step in
   // kv_rows, row cu_kv[e] + j for key j of entry e: the key's first dim_rows elements at column kvh * dim_rows,
   // its values at column v_off + kvh * dv.  The key's other dk - dim_rows elements are shared by the heads and
@@ -283,6 +285,8 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
                                       const float* __restrict__ sinks, int nq, int nkv, int dk, int dv,
                                       int page_size, float scale, int window, int nsplit, int kv_chunk,
                                       float* __restrict__ part_o, float* __restrict__ part_ml, int row_tiles) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int e = blockIdx.z, kvh = blockIdx.y / row_tiles, slice = blockIdx.x;
   const int r0 = (blockIdx.y % row_tiles) * 16;             // the block's 16 rows of the entry's q_len * G
@@ -473,7 +477,7 @@ static int launch_mma(dim3 grid, size_t smem, cudaStream_t stream, const float* 
                       const int* cu_kv = nullptr, int dim_rows = 0, int v_off = 0, int page_skip = 0) {
   auto kern = paged_attention_general_mma_kernel<TO, NT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  kern<<<grid, kMmaWarps * 32, smem, stream>>>(q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out, block_table,
+  launch_pdl(kern, dim3(grid), dim3(kMmaWarps * 32), smem, stream, q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out, block_table,
                                                table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale,
                                                window, nbuf, kv_rows, ld_rows, cu_kv, dim_rows, v_off, page_skip);
   return launched();
@@ -555,7 +559,7 @@ extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k
   do {                                                                                                             \
     auto kern = paged_attention_general_decode_kernel<TO, NTW>;                                                    \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-    kern<<<grid, kMmaWarps * 32, smem, stream>>>(q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out,          \
+    launch_pdl(kern, dim3(grid), dim3(kMmaWarps * 32), smem, stream, q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out,          \
                                                  block_table, table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, \
                                                  page_size, scale, window, nsplit, kv_chunk, part_o, part_ml,      \
                                                  row_tiles);                                                       \

@@ -31,6 +31,8 @@ __global__ void delta_prepare_kernel(const TP* __restrict__ proj, long long ldp,
                                      float* __restrict__ beta_out, float* __restrict__ decay_out,
                                      float* __restrict__ qk_out, int H, int G, int dk, int dv, int taps,
                                      float unit_eps) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   extern __shared__ float ch[];                              // [C] convolved and activated channels of this token
   const int t = blockIdx.x;
   const int C = 2 * G * dk + H * dv;
@@ -82,6 +84,8 @@ template <typename TP>
 __global__ void delta_conv_carry_kernel(const TP* __restrict__ proj, long long ldp, float* __restrict__ state,
                                         long long state_stride, long long carry_off, const int* __restrict__ cu_q,
                                         const int* __restrict__ slots, int n_entries, int C, int taps) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (long long)n_entries * C) return;
   const int e = (int)(i / C), c = (int)(i % C);
@@ -121,6 +125,8 @@ __global__ void __launch_bounds__(kColumnsPerBlock* kLanesPerColumn)
 delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ beta, const float* __restrict__ decay,
                         const float* __restrict__ qk, float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
                         const int* __restrict__ slots, float* __restrict__ o_out, int H, int G, int dk, int dv) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   constexpr int DKP = RPL * kLanesPerColumn;                 // rows held in shared memory (zero beyond dk)
   constexpr int ROW = 2 * DKP + kColumnsPerBlock + 4;        // k | q | v of the block's columns | beta, g, q.k, -
   extern __shared__ __align__(16) float stage[];            // [2][kChunk][ROW]
@@ -220,6 +226,8 @@ template <typename TP, typename TA>
 __global__ void delta_output_kernel(const float* __restrict__ o, const float* __restrict__ norm_w, float eps,
                                     const TP* __restrict__ proj, long long ldp, int gate_off, TA* __restrict__ out,
                                     int H, int dv) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int h = warp; h < H; h += nwarps) {
     const float* row = o + ((size_t)t * H + h) * dv;
@@ -256,12 +264,12 @@ extern "C" int srlm_delta_prepare(const void* proj, int proj_dtype, long long ld
   SRLM_DISPATCH_ACT(proj_dtype, TP, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(delta_prepare_kernel<TP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    delta_prepare_kernel<TP><<<T, 256, smem, stream>>>((const TP*)proj, ldp, conv_w, a_log, dt_bias, state, state_stride,
+    launch_pdl(delta_prepare_kernel<TP>, dim3(T), dim3(256), smem, stream, (const TP*)proj, ldp, conv_w, a_log, dt_bias, state, state_stride,
                                                        entry_of_token, cu_q, slots, qkv_out, beta_out, decay_out, qk_out,
                                                        H, G, dk, dv, taps, unit_eps);
     if (taps > 1) {
       const long long n = (long long)n_entries * C;
-      delta_conv_carry_kernel<TP><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+      launch_pdl(delta_conv_carry_kernel<TP>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 
           (const TP*)proj, ldp, state, state_stride, (long long)H * dk * dv, cu_q, slots, n_entries, (int)C, taps);
     }
   });
@@ -282,7 +290,7 @@ extern "C" int srlm_delta_recurrence(const float* qkv, const float* beta, const 
     const size_t smem = (size_t)2 * kChunk * (2 * R * kLanesPerColumn + kColumnsPerBlock + 4) * sizeof(float);   \
     if (smem > 48 * 1024)                                                                                        \
       cudaFuncSetAttribute(delta_recurrence_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    delta_recurrence_kernel<R><<<grid, threads, smem, stream>>>(qkv, beta, decay, qk, state, state_stride, cu_q, \
+    launch_pdl(delta_recurrence_kernel<R>, dim3(grid), dim3(threads), smem, stream, qkv, beta, decay, qk, state, state_stride, cu_q, \
                                                                 slots, o_out, H, G, dk, dv);                     \
   } while (0)
   if (rpl <= 4) SRLM_DELTA_CASE(4);
@@ -302,7 +310,7 @@ extern "C" int srlm_delta_output(const float* o, const float* norm_w, float eps,
     return refuse(ST_BAD_SIZE, "delta_output: H=%d dv=%d gate_off=%d ldp=%lld", H, dv, gate_off, ldp);
   const int threads = 32 * (H < 8 ? H : 8);
 #define SRLM_DELTA_OUT(TP, TA)                                                                                    \
-  delta_output_kernel<TP, TA><<<T, threads, 0, stream>>>(o, norm_w, eps, (const TP*)proj, ldp, gate_off, (TA*)out, H, dv)
+  launch_pdl(delta_output_kernel<TP, TA>, dim3(T), dim3(threads), 0, stream, o, norm_w, eps, (const TP*)proj, ldp, gate_off, (TA*)out, H, dv)
   if (proj_dtype == DT_F32 && out_dtype == DT_F32) SRLM_DELTA_OUT(float, float);
   else if (proj_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_DELTA_OUT(float, bf16);
   else if (proj_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_DELTA_OUT(bf16, bf16);

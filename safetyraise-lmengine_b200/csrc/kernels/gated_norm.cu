@@ -16,6 +16,8 @@ __global__ void gated_postnorm_add_kernel(float* __restrict__ residual, const TA
                                           const float* __restrict__ post_w, float eps,
                                           const float* __restrict__ next_w, float next_eps, TA* __restrict__ next_out,
                                           int H) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   extern __shared__ float row[];
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * H;
@@ -59,7 +61,7 @@ extern "C" int srlm_gated_postnorm_add(float* residual, const void* sub, const v
   SRLM_DISPATCH_ACT(act_dtype, TA, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(gated_postnorm_add_kernel<TA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    gated_postnorm_add_kernel<TA><<<T, block, smem, stream>>>(residual, (const TA*)sub, (const TA*)gate, gate_bias,
+    launch_pdl(gated_postnorm_add_kernel<TA>, dim3(T), dim3(block), smem, stream, residual, (const TA*)sub, (const TA*)gate, gate_bias,
                                                               post_w, eps, next_w, next_eps, (TA*)next_out, H);
   });
   return launched();

@@ -24,6 +24,8 @@ __global__ void latent_append_kernel(const TP* __restrict__ proj, long long ldp,
                                      const float* __restrict__ norm_w, float eps, const float* __restrict__ cos_t,
                                      const float* __restrict__ sin_t, int pairs, TC* __restrict__ cache,
                                      const int* __restrict__ kv_slot, int rank, int rot) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const TP* p = proj + (size_t)t * ldp + c_off;
@@ -87,6 +89,8 @@ __global__ void __launch_bounds__(kProductWarps * 32)
 latent_absorb_kernel(const TP* __restrict__ proj, long long ldp, const TW* __restrict__ uk,
                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int pairs,
                      float* __restrict__ q_out, int T, int heads, int dim, int rot, int rank) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   extern __shared__ float sh[];                              // [kTokTile][dim] | [warps][kTokTile][32]
   float* q_s = sh;
   float* red = sh + kTokTile * dim;
@@ -126,6 +130,8 @@ template <typename TP, typename TW, typename TA>
 __global__ void __launch_bounds__(kProductWarps * 32)
 latent_expand_kernel(const float* __restrict__ o_lat, const TW* __restrict__ uv_t, const TP* __restrict__ proj,
                      long long ldp, int g_off, TA* __restrict__ out, int T, int heads, int rank, int dv) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   extern __shared__ float sh[];                              // [kTokTile][rank] | [warps][kTokTile][32]
   float* o_s = sh;
   float* red = sh + kTokTile * rank;
@@ -159,6 +165,8 @@ template <typename TC>
 __global__ void latent_gather_kernel(const TC* __restrict__ cache, TC* __restrict__ dst,
                                      const int* __restrict__ block_table, int table_stride,
                                      const int* __restrict__ cu_kv, int page_size, int width, int rank) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   const int e = blockIdx.y;
   const int n = cu_kv[e + 1] - cu_kv[e];
   const int* table = block_table + (size_t)e * table_stride;
@@ -174,6 +182,8 @@ template <typename TP>
 __global__ void latent_rotate_q_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t, int pairs, float* __restrict__ q_out,
                                        int heads, int dim, int rot) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   const int t = blockIdx.x, hd = dim + rot;
   for (int idx = threadIdx.x; idx < heads * hd; idx += blockDim.x) {
     const int h = idx / hd, i = idx - h * hd;
@@ -193,6 +203,8 @@ __global__ void latent_rotate_q_kernel(const TP* __restrict__ proj, long long ld
 template <typename TP, typename TA>
 __global__ void head_gate_kernel(const float* __restrict__ in, const TP* __restrict__ proj, long long ldp, int g_off,
                                  TA* __restrict__ out, int heads, int dv) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
   const int t = blockIdx.x;
   for (int idx = threadIdx.x; idx < heads * dv; idx += blockDim.x) {
     const float g = g_off >= 0 ? 1.f / (1.f + expf(-to_float(proj[(size_t)t * ldp + g_off + idx / dv]))) : 1.f;
@@ -220,7 +232,7 @@ extern "C" int srlm_latent_append(const void* proj, int proj_dtype, long long ld
   if (rank <= 0 || rot < 0 || 2 * pairs > rot || c_off < 0 || ldp < c_off + rank + rot || !(eps > 0.f) ||
       (pairs > 0 && (!cos_t || !sin_t)))
     return refuse(ST_BAD_SIZE, "latent_append: rank=%d rot=%d pairs=%d c_off=%d ldp=%lld", rank, rot, pairs, c_off, ldp);
-  SRLM_LATENT_TYPES(proj_dtype, cache_dtype, (latent_append_kernel<TP, TW><<<T, 128, 0, stream>>>(
+  SRLM_LATENT_TYPES(proj_dtype, cache_dtype, (launch_pdl(latent_append_kernel<TP, TW>, dim3(T), dim3(128), 0, stream, 
       (const TP*)proj, ldp, c_off, norm_w, eps, cos_t, sin_t, pairs, (TW*)cache, kv_slot, rank, rot)));
   return launched();
 }
@@ -235,7 +247,7 @@ extern "C" int srlm_latent_absorb(const void* proj, int proj_dtype, long long ld
     return refuse(ST_BAD_SIZE, "latent_absorb: heads=%d dim=%d rot=%d rank=%d pairs=%d ldp=%lld", heads, dim, rot, rank,
                   pairs, ldp);
   dim3 grid((T + kTokTile - 1) / kTokTile, heads, (rank + kColTile - 1) / kColTile);
-  SRLM_LATENT_TYPES(proj_dtype, w_dtype, (latent_absorb_kernel<TP, TW><<<grid, kProductWarps * 32, smem, stream>>>(
+  SRLM_LATENT_TYPES(proj_dtype, w_dtype, (launch_pdl(latent_absorb_kernel<TP, TW>, dim3(grid), dim3(kProductWarps * 32), smem, stream, 
       (const TP*)proj, ldp, (const TW*)uk, cos_t, sin_t, pairs, q_out, T, heads, dim, rot, rank)));
   return launched();
 }
@@ -252,7 +264,7 @@ extern "C" int srlm_latent_expand(const float* o_lat, const void* uv_t, int w_dt
   do {                                                                                                           \
     auto kern = latent_expand_kernel<TP, TW, TA>;                                                                \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    kern<<<grid, kProductWarps * 32, smem, stream>>>(o_lat, (const TW*)uv_t, (const TP*)proj, ldp, g_off, (TA*)out, T, heads,   \
+    launch_pdl(kern, dim3(grid), dim3(kProductWarps * 32), smem, stream, o_lat, (const TW*)uv_t, (const TP*)proj, ldp, g_off, (TA*)out, T, heads,   \
                                       rank, dv);                                                                 \
   } while (0)
   if (out_dtype == DT_F32) SRLM_LATENT_TYPES(proj_dtype, w_dtype, SRLM_EXPAND(float));
@@ -269,7 +281,7 @@ extern "C" int srlm_latent_gather(const void* cache, int cache_dtype, void* dst,
   if (rank <= 0 || width < rank || page_size <= 0 || n_entries > 65535)
     return refuse(ST_BAD_SIZE, "latent_gather: rank=%d width=%d page_size=%d entries=%d", rank, width, page_size, n_entries);
   dim3 grid((unsigned)(max_kv_len < 4096 ? max_kv_len : 4096), (unsigned)n_entries);
-  SRLM_DISPATCH_ACT(cache_dtype, TC, (latent_gather_kernel<TC><<<grid, 64, 0, stream>>>(
+  SRLM_DISPATCH_ACT(cache_dtype, TC, (launch_pdl(latent_gather_kernel<TC>, dim3(grid), dim3(64), 0, stream, 
       (const TC*)cache, (TC*)dst, block_table, table_stride, cu_kv, page_size, width, rank)));
   return launched();
 }
@@ -281,7 +293,7 @@ extern "C" int srlm_latent_rotate_q(const void* proj, int proj_dtype, long long 
   if (heads <= 0 || dim <= 0 || rot < 0 || 2 * pairs > rot || ldp < (long long)heads * (dim + rot) ||
       (pairs > 0 && (!cos_t || !sin_t)))
     return refuse(ST_BAD_SIZE, "latent_rotate_q: heads=%d dim=%d rot=%d pairs=%d ldp=%lld", heads, dim, rot, pairs, ldp);
-  SRLM_DISPATCH_ACT(proj_dtype, TP, (latent_rotate_q_kernel<TP><<<T, 256, 0, stream>>>(
+  SRLM_DISPATCH_ACT(proj_dtype, TP, (launch_pdl(latent_rotate_q_kernel<TP>, dim3(T), dim3(256), 0, stream, 
       (const TP*)proj, ldp, cos_t, sin_t, pairs, q_out, heads, dim, rot)));
   return launched();
 }
@@ -291,7 +303,7 @@ extern "C" int srlm_head_gate(const float* in, const void* proj, int proj_dtype,
   if (T <= 0) return ST_OK;
   if (heads <= 0 || dv <= 0 || (g_off >= 0 && ldp < g_off + heads))
     return refuse(ST_BAD_SIZE, "head_gate: heads=%d dv=%d g_off=%d ldp=%lld", heads, dv, g_off, ldp);
-#define SRLM_GATE(TP, TA) head_gate_kernel<TP, TA><<<T, 256, 0, stream>>>(in, (const TP*)proj, ldp, g_off, (TA*)out, heads, dv)
+#define SRLM_GATE(TP, TA) launch_pdl(head_gate_kernel<TP, TA>, dim3(T), dim3(256), 0, stream, in, (const TP*)proj, ldp, g_off, (TA*)out, heads, dv)
   if (proj_dtype == DT_F32 && out_dtype == DT_F32) SRLM_GATE(float, float);
   else if (proj_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_GATE(float, bf16);
   else if (proj_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_GATE(bf16, bf16);
