@@ -2,6 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--workload decode|mixed]
+    python bench.py --design nekedra [--design-size 2048|4096]
 
 A "step" is one decode step: every request of the batch gets its next token.
 The default run has the sizes of the 8B configuration (36 layers, hidden 4096,
@@ -30,6 +31,11 @@ with 4,096 tokens of context, one 2,048-token prefill), ``--shape 14b`` (whose
 default workload is ``mixed``) 32 requests with prompts of 128 to 3,072 tokens
 prefilled in portions of up to 512 tokens beside the decoding ones, through the
 scheduler.
+
+``--design nekedra`` leaves all of that aside and prints another line: prefill
+and decode of four-layer Nekedra stacks (each mixer alone, and mixed) beside the
+Qwen3 decoder at equal width, heads and feed-forward size, with the kernels an
+eager step spends its time in (``run_design``).
 """
 from __future__ import annotations
 
