@@ -223,8 +223,9 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
 // (1 - lambda) v + lambda kept; k and the final v go to the pages (kv_slot[t] = page * page_size + offset).
 template <typename TP, typename TC>
 __global__ void attention_bias_append_kernel(const TP* __restrict__ proj, long long ldp, const float* __restrict__ bias,
-                                             float* __restrict__ q_out, TC* __restrict__ k_cache,
-                                             TC* __restrict__ v_cache, const int* __restrict__ kv_slot,
+                                             float* __restrict__ q_out, bf16* __restrict__ q_out_bf16,
+                                             TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+                                             const int* __restrict__ kv_slot,
                                              float* __restrict__ v_keep, const float* __restrict__ lambda,
                                              int mix_mode, int write_kv, int nq, int nkv, int dk, int dv,
                                              int page_size) {
@@ -233,8 +234,11 @@ __global__ void attention_bias_append_kernel(const TP* __restrict__ proj, long l
   const int t = blockIdx.x;
   const TP* p = proj + (size_t)t * ldp;
   const int nqd = nq * dk, nkd = nkv * dk, nvd = nkv * dv;
-  for (int c = threadIdx.x; c < nqd; c += blockDim.x)
-    q_out[(size_t)t * nqd + c] = to_float(p[c]) + (bias ? bias[c] : 0.f);
+  for (int c = threadIdx.x; c < nqd; c += blockDim.x) {
+    const float v = to_float(p[c]) + (bias ? bias[c] : 0.f);
+    if (q_out_bf16) q_out_bf16[(size_t)t * nqd + c] = __float2bfloat16_rn(v);     // for kernels that take bfloat16 queries
+    else q_out[(size_t)t * nqd + c] = v;
+  }
   const int slot = kv_slot[t];
   const size_t page = slot / page_size, off = slot % page_size;
   if (write_kv) {
@@ -333,7 +337,7 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
 // proj: [T, ldp] in proj_dtype, columns q (nq * dk), k (nkv * dk), v (nkv * dv); bias: float32 over the
 // same columns or null.  mix_mode 0: v as it is; 1: also kept in v_keep; 2: mixed with v_keep by lambda[0].
 extern "C" int srlm_attention_bias_append(const void* proj, int proj_dtype, long long ldp, const float* bias,
-                                          float* q_out, void* k_cache, void* v_cache, int cache_dtype,
+                                          void* q_out, int q_dtype, void* k_cache, void* v_cache, int cache_dtype,
                                           const int* kv_slot, float* v_keep, const float* lambda, int mix_mode,
                                           int write_kv, int T, int nq, int nkv, int dk, int dv, int page_size,
                                           cudaStream_t stream) {
@@ -343,7 +347,7 @@ extern "C" int srlm_attention_bias_append(const void* proj, int proj_dtype, long
     return refuse(ST_BAD_SIZE, "attention_bias_append: nq=%d nkv=%d dk=%d dv=%d ldp=%lld mix_mode=%d", nq, nkv, dk, dv,
                   ldp, mix_mode);
 #define SRLM_APPEND(TP, TC)                                                                                       \
-  launch_pdl(attention_bias_append_kernel<TP, TC>, dim3(T), dim3(256), 0, stream, (const TP*)proj, ldp, bias, q_out, (TC*)k_cache,    \
+  launch_pdl(attention_bias_append_kernel<TP, TC>, dim3(T), dim3(256), 0, stream, (const TP*)proj, ldp, bias, q_dtype == DT_F32 ? (float*)q_out : nullptr, q_dtype == DT_BF16 ? (bf16*)q_out : nullptr, (TC*)k_cache,    \
                                                               (TC*)v_cache, kv_slot, v_keep, lambda, mix_mode,   \
                                                               write_kv, nq, nkv, dk, dv, page_size)
   if (proj_dtype == DT_F32 && cache_dtype == DT_F32) SRLM_APPEND(float, float);

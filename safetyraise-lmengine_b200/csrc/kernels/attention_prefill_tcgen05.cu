@@ -65,6 +65,9 @@ struct Args {
   int kv_chunk;
   float* part_o;
   float* part_ml;
+  // optional, one per query head: a term exp(sink) in the softmax denominator that has no key and no value.
+  // It is the state a row's running softmax starts from (maximum = sink, sum = 1); with key slices, slice 0's.
+  const float* sinks;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -509,6 +512,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
     const int pos_max = start + (min(r_first[i] + BR, r_end) - 1) / g;
     const int lo_max = a.window > 0 ? max(0, pos_max - a.window + 1) : 0;
     float m_run = -CUDART_INF_F, l_run = 0.f;
+    if (a.sinks && (!sliced || blockIdx.y == 0)) {
+      const int rs = min(r, r_end - 1);
+      m_run = a.sinks[kvh * g + rs % g] * 1.4426950408889634f;      // in log2 units, like the scaled scores
+      l_run = 1.f;
+    }
     bool ok = true;
     for (int t = 0; t < n_tiles && ok; ++t) {
       const int jb = jb0 + t * KT;
@@ -536,8 +544,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
           for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
           tmem_st16(o_addr + c, v);
         }
-        l_run *= alpha;
       }
+      if (m_new != m_run) l_run *= ex2(m_run - m_new);      // also before the first tile: a sink's share of the sum
       m_run = m_new;
       const float base = m_run == -CUDART_INF_F ? 0.f : m_run;
       l_run += full ? row_exp<false>(s_addr, srow, a.scale_log2, base, 0, KT)
@@ -711,12 +719,12 @@ extern "C" int srlm_attention_prefill_tcgen05_takes(int hd, int page_size) {
 // (nq / nkv); tiles_per_block is 1 or 2.  nsplit > 1 cuts the keys into slices of kv_chunk (a multiple of
 // 128) with a block each; part_o then holds n_work * 2 * nkv * nsplit * 128 * 128 floats and part_ml
 // n_work * 2 * nkv * nsplit * 128 * 2, and a second kernel adds the slices.
-extern "C" int srlm_paged_attention_prefill_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                                    long long num_pages, const int* block_table, int table_stride,
-                                                    const int* cu_q, const int* kv_lens, const int* work, int n_work,
-                                                    int nq, int nkv, int hd, int page_size, float scale, int window,
-                                                    int tiles_per_block, int nsplit, int kv_chunk, float* part_o,
-                                                    float* part_ml, int* err_flag, cudaStream_t stream) {
+static int prefill_tcgen05_entry(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                 long long num_pages, const int* block_table, int table_stride,
+                                 const int* cu_q, const int* kv_lens, const int* work, int n_work,
+                                 int nq, int nkv, int hd, int page_size, float scale, int window,
+                                 int tiles_per_block, int nsplit, int kv_chunk, float* part_o,
+                                 float* part_ml, const float* sinks, int* err_flag, cudaStream_t stream) {
   if (n_work <= 0) return ST_OK;
   if (nsplit < 1) nsplit = 1;
   if (nsplit > 1 && (nsplit > 32 || kv_chunk <= 0 || kv_chunk % fmha::KT || !part_o || !part_ml))
@@ -741,7 +749,7 @@ extern "C" int srlm_paged_attention_prefill_tcgen05(const void* q, const void* k
     configured = true;
   }
   fmha::Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, work, nq, nkv, page_size,
-               tiles_per_block, scale * 1.4426950408889634f, window, err_flag, nsplit, kv_chunk, part_o, part_ml};
+               tiles_per_block, scale * 1.4426950408889634f, window, err_flag, nsplit, kv_chunk, part_o, part_ml, sinks};
   launch_pdl(fmha::attention_prefill_tcgen05_kernel, dim3(n_work * nkv, nsplit), dim3(fmha::THREADS), SMEM, stream,
              *mk, *mv, a);
   if (nsplit > 1)
@@ -749,3 +757,27 @@ extern "C" int srlm_paged_attention_prefill_tcgen05(const void* q, const void* k
   return launched();
 }
 
+
+extern "C" int srlm_paged_attention_prefill_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                                    long long num_pages, const int* block_table, int table_stride,
+                                                    const int* cu_q, const int* kv_lens, const int* work, int n_work,
+                                                    int nq, int nkv, int hd, int page_size, float scale, int window,
+                                                    int tiles_per_block, int nsplit, int kv_chunk, float* part_o,
+                                                    float* part_ml, int* err_flag, cudaStream_t stream) {
+  return prefill_tcgen05_entry(q, k_cache, v_cache, out, num_pages, block_table, table_stride, cu_q, kv_lens, work, n_work,
+                               nq, nkv, hd, page_size, scale, window, tiles_per_block, nsplit, kv_chunk, part_o, part_ml,
+                               nullptr, err_flag, stream);
+}
+
+// The same with a sink per query head (float32 [nq]) in every row's softmax denominator.
+extern "C" int srlm_paged_attention_prefill_tcgen05_sinks(const void* q, const void* k_cache, const void* v_cache,
+                                                          void* out, long long num_pages, const int* block_table,
+                                                          int table_stride, const int* cu_q, const int* kv_lens,
+                                                          const int* work, int n_work, int nq, int nkv, int hd,
+                                                          int page_size, float scale, int window, int tiles_per_block,
+                                                          int nsplit, int kv_chunk, float* part_o, float* part_ml,
+                                                          const float* sinks, int* err_flag, cudaStream_t stream) {
+  return prefill_tcgen05_entry(q, k_cache, v_cache, out, num_pages, block_table, table_stride, cu_q, kv_lens, work, n_work,
+                               nq, nkv, hd, page_size, scale, window, tiles_per_block, nsplit, kv_chunk, part_o, part_ml,
+                               sinks, err_flag, stream);
+}

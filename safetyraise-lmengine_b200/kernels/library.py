@@ -73,6 +73,7 @@ class KernelLibrary:
         self.split_general_attention = True     # decode steps of the general attention: the keys in slices
         self.general_attention_on_tensor_cores = True   # its prompts and portions: mma.sync, when the sizes fit
         self.latent_prompts_in_head_space = True        # latent attention: prompts form per-head keys and values
+        self.sinks_in_tcgen05_prefill = True            # attention with sinks, heads of 128: prompts on the tcgen05 kernel
 
     @property
     def lib(self):
@@ -469,19 +470,27 @@ class KernelLibrary:
 
     def paged_attention_prefill_tcgen05(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, work, nq, nkv,
                                         hd, page_size, scale, window=0, tiles_per_block=2, nsplit=1, kv_chunk=0,
-                                        part_o=None, part_ml=None):
+                                        part_o=None, part_ml=None, sinks=None):
         """Rows-split attention on tcgen05 tensor cores with accumulators in tensor memory (head size
         128; page_size 8..64 a power of two, or a multiple of 128); work: int32 [n, 2] (entry, block of
         tiles_per_block x 128 rows), tiles_per_block 1 or 2.  nsplit > 1: the keys in slices of kv_chunk
         (a multiple of 128), a block each, added by a second kernel; part_o float32
         [n * 2 * nkv * nsplit * 128, 128] and part_ml [.., 2] are their workspace."""
         err = self._gemm_state(q.device)[1]
-        self._check(self.lib.srlm_paged_attention_prefill_tcgen05(
-            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
-            C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
-            C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
-            C.c_int(tiles_per_block), C.c_int(nsplit), C.c_int(kv_chunk), _ptr(part_o), _ptr(part_ml), _ptr(err),
-            _stream()), "paged_attention_prefill_tcgen05")
+        if sinks is not None:       # float32 [nq]: one more term exp(sink) in each head's softmax denominator
+            self._check(self.lib.srlm_paged_attention_prefill_tcgen05_sinks(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
+                C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
+                C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
+                C.c_int(tiles_per_block), C.c_int(nsplit), C.c_int(kv_chunk), _ptr(part_o), _ptr(part_ml), _ptr(sinks),
+                _ptr(err), _stream()), "paged_attention_prefill_tcgen05")
+        else:
+            self._check(self.lib.srlm_paged_attention_prefill_tcgen05(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
+                C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
+                C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
+                C.c_int(tiles_per_block), C.c_int(nsplit), C.c_int(kv_chunk), _ptr(part_o), _ptr(part_ml), _ptr(err),
+                _stream()), "paged_attention_prefill_tcgen05")
         if nsplit > 1:
             self.launches += 1           # the kernel that adds the slices
 
@@ -621,11 +630,21 @@ class KernelLibrary:
                                           page_size, scale, window, chunk, nsplit, part_o, part_ml, cluster=cluster)
         return True
 
+    def sinks_on_tcgen05(self, ctx, dtype, nq, nkv, hd, dv, page_size) -> bool:
+        """Whether paged_attention(..., sinks=...) can serve this step: only its tensor-memory rows kernel knows
+        sinks (head size 128 for keys and values, bfloat16, some entry of more than 16 rows)."""
+        return (dtype == torch.bfloat16 and hd == dv and ctx.max_q_len * (nq // nkv) > 16
+                and not self.force_simt_attention and not self.force_mma_sync_prefill and self.sinks_in_tcgen05_prefill
+                and bool(self.lib.srlm_attention_prefill_tcgen05_takes(C.c_int(hd), C.c_int(page_size))))
+
     def paged_attention(self, ctx, q, k_cache, v_cache, out, block_table, nq, nkv, hd, page_size, scale,
-                        window=0):
+                        window=0, sinks=None):
         """The product path's attention over the cache for the batch of ``ctx``: tensor cores for
         bfloat16 (keys-split when every entry is a few rows, rows-split otherwise), float32 FMA for
-        the float32 path."""
+        the float32 path.  sinks (float32 [nq]): only where sinks_on_tcgen05 says so; every entry then goes
+        to the rows kernel."""
+        if sinks is not None and not self.sinks_on_tcgen05(ctx, q.dtype, nq, nkv, hd, hd, page_size):
+            raise ShapeError("paged_attention: sinks are served by the tensor-memory rows kernel only")
         if q.dtype != torch.bfloat16 or hd % 16 or hd > 256 or self.force_simt_attention:
             self.paged_attention_simt(q, k_cache, v_cache, out, block_table, ctx.entry_of_token, ctx.positions,
                                       nq, nkv, hd, page_size, scale, window)
@@ -676,7 +695,7 @@ class KernelLibrary:
         # the step faster in two launches; 32 requests of 128 to 3,200 tokens, 1.5 % slower.
         short = list(range(head)) + list(range(tail, n))
         enough = self.sm_count(q.device) if self.split_mixed_min_blocks is None else self.split_mixed_min_blocks
-        if self.split_mixed_attention and ctx.max_q_len > 1 and short and len(short) * nkv >= enough:
+        if sinks is None and self.split_mixed_attention and ctx.max_q_len > 1 and short and len(short) * nkv >= enough:
             lens = [ctx.host["kv_lens"][e] for e in short]
             if max(lens) * len(lens) > 1.5 * sum(lens):
                 short = []
@@ -729,7 +748,7 @@ class KernelLibrary:
                 part_ml = ctx.workspace.get("attn.rows_part_ml", slabs, 2, torch.float32, reserve=0)
             self.paged_attention_prefill_tcgen05(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work,
                                                  nq, nkv, hd, page_size, scale, window, tiles, nsplit, chunk, part_o,
-                                                 part_ml)
+                                                 part_ml, sinks=sinks)
             return
         tma = (hd in (64, 128) and self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size))
                and not self.force_cp_async_decode)
@@ -832,13 +851,14 @@ class KernelLibrary:
 
     def attention_bias_append(self, proj, bias, q_out, k_cache, v_cache, kv_slot, nq, nkv, dk, dv, v_keep=None,
                               lam=None, mix_mode=0, write_kv=True):
-        """From a stacked q | k | v projection [T, >= nq dk + nkv (dk + dv)]: q + bias to q_out (float32), k + bias
+        """From a stacked q | k | v projection [T, >= nq dk + nkv (dk + dv)]: q + bias to q_out (float32, or
+        bfloat16 for the kernels that take their queries so), k + bias
         and v + bias to the pages.  mix_mode 1 also keeps v in v_keep (float32 [T, nkv dv]); mix_mode 2 writes
         (1 - lam) v + lam v_keep instead of v (lam: float32 [1] on the device)."""
         T = proj.shape[0]
         self._check(self.lib.srlm_attention_bias_append(
-            _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(bias), _ptr(q_out), _ptr(k_cache),
-            _ptr(v_cache), dtype_code(k_cache.dtype), _ptr(kv_slot), _ptr(v_keep), _ptr(lam), C.c_int(mix_mode),
+            _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), _ptr(bias), _ptr(q_out),
+            dtype_code(q_out.dtype), _ptr(k_cache), _ptr(v_cache), dtype_code(k_cache.dtype), _ptr(kv_slot), _ptr(v_keep), _ptr(lam), C.c_int(mix_mode),
             C.c_int(int(write_kv)), C.c_int(T), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
             C.c_int(k_cache.shape[2]), _stream()), "attention_bias_append")
 

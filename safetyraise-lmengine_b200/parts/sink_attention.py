@@ -64,7 +64,12 @@ class SinkAttention(Part):
         # the projection's result stays float32: the scores are float32 products of it
         qkv = self.qkv(ctx, x, "sink_attn.qkv", out_dtype=torch.float32)
         k_pool, v_pool, group = ctx.cache.kv_of_entry(run_step.cache)
-        q = ctx.workspace.get("sink_attn.q", T, s.heads * s.head_dim, torch.float32)
+        # prompts with heads of 128 for keys and values: the framework's tensor-memory kernel, which takes its
+        # queries in bfloat16 and starts every row's softmax from the head's sink
+        page_size = k_pool.shape[2]
+        on_tcgen05 = (v_pool is not None and not s.window and ctx.max_q_len > 4 and s.sink
+                      and ops.sinks_on_tcgen05(ctx, ctx.dtype, s.heads, s.kv_heads, s.head_dim, s.v_head_dim, page_size))
+        q = ctx.workspace.get("sink_attn.q", T, s.heads * s.head_dim, ctx.dtype if on_tcgen05 else torch.float32)
         keep, mode = None, 0
         if s.value_mix:
             key = ("kept_values", s.kv_heads * s.v_head_dim)
@@ -80,6 +85,10 @@ class SinkAttention(Part):
         ops.attention_bias_append(qkv, self.bias, q, k_pool, v_pool, ctx.kv_slot[group], s.heads, s.kv_heads,
                                   s.head_dim, s.v_head_dim, keep, self.lam, mode, run_step.writes_cache)
         attended = ctx.workspace.get("sink_attn.out", T, s.heads * s.v_head_dim, ctx.dtype)
+        if on_tcgen05:
+            ops.paged_attention(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], s.heads, s.kv_heads,
+                                s.head_dim, page_size, s.softmax_scale, 0, sinks=self.sink)
+            return self.out(ctx, attended, "sink_attn.proj")
         ops.paged_attention_general(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], self.sink, s.heads,
                                     s.kv_heads, s.head_dim, s.v_head_dim, s.softmax_scale, s.window or 0)
         return self.out(ctx, attended, "sink_attn.proj")

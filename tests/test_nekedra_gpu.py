@@ -53,6 +53,9 @@ CONFIGS = {
                     attention(heads=4, kv_heads=2, dim=32, vdim=64), latent(heads=2, dim=32, rot_dim=16, dims=8, rank=64, vdim=16),
                     delta(heads=2, kv_heads=1, dim=272, vdim=16, conv=2)],       # a state too wide for a lane's registers
                    width=128, vocab=260),
+    # heads of 128 for keys and values: prompts run the tensor-memory kernel, each row's softmax starting from its sink
+    "heads128": config([attention(heads=4, kv_heads=2, dim=128, vdim=128), attention(heads=2, kv_heads=2, dim=128, vdim=128)],
+                       width=128, vocab=210),
     # sizes that are 1, odd or no multiple of 8: a width that the tensor-core products do not take
     "odd": config([delta(heads=1, kv_heads=1, dim=40, vdim=33, conv=1), latent(heads=1, dim=12, rot_dim=6, dims=2, rank=20, vdim=9),
                    attention(heads=3, kv_heads=1, dim=24, vdim=8), attention(heads=2, kv_heads=1, dim=8, vdim=8)],
@@ -256,6 +259,18 @@ def test_long_decoding(model, dtype):
     reqs = requests_for(model[2], lens=(300,), seed=3)
     eng = build(model[1], dtype, num_pages=24, page_size=16)
     got = replay(eng, cut_bulk_tail("r0", reqs["r0"], 260))
+    check(got, model, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_long_prompt_in_portions(model, dtype):
+    """700 tokens in portions of 48: the later portions stand behind hundreds of cached keys (the rows kernels cut
+    such keys into slices, and only the first slice may start from the sink)."""
+    if model[0] not in ("heads128", "wide", "attention"):
+        pytest.skip("one configuration of each attention kernel is enough")
+    reqs = requests_for(model[2], lens=(700,), seed=6)
+    eng = build(model[1], dtype, num_pages=48, page_size=16)
+    got = replay(eng, cut_portions("r0", reqs["r0"], sizes=(48,)))
     check(got, model, reqs, dtype)
 
 
