@@ -1,5 +1,7 @@
-"""Pre-norm residual block: r = x + mixer(norm(x)); x' = r + ff(norm(r)).
-src/model/native.rs:526-562.
+"""The arrangements of norms, mixer and feed-forward around the residual stream.
+
+``pre_norm``: r = x + mixer(norm(x)); x' = r + ff(norm(r))  (src/model/native.rs:526-562).
+``sandwich_gated``: a norm before and after each sublayer and a learned gate on its result (see the class).
 
 The residual stream is a float32 tensor updated in place.  A block does not add
 its feed-forward output itself: it returns it as *pending*, and the next norm
@@ -10,8 +12,10 @@ from __future__ import annotations
 from typing import List
 
 from ..config.spec import LayerSpec, RunStep
-from ..weights.loader import TensorDecl
+from ..kernels import ops
+from ..weights.loader import MATRIX, VECTOR, TensorDecl
 from .base import FEED_FORWARDS, MIXERS, NORMS, Block, NormedInput, lookup, register_block
+from .linear import Linear
 
 
 @register_block("pre_norm")
@@ -86,7 +90,6 @@ class SandwichGatedBlock(Block):
     residual stream and the norm ahead of the next sublayer are one kernel (ops.gated_postnorm_add)."""
 
     def __init__(self, spec: LayerSpec, tensors: dict, mctx):
-        from .linear import Linear
         p = spec.weight_prefix
         self.spec = spec
         norm = lambda ns, name: lookup(NORMS, ns.kind, "norm")(ns, p + name, tensors, mctx)
@@ -108,7 +111,6 @@ class SandwichGatedBlock(Block):
 
     @classmethod
     def tensor_decls(cls, spec: LayerSpec, prefix: str = "") -> List[TensorDecl]:
-        from ..weights.loader import MATRIX, VECTOR
         p, H = spec.weight_prefix, spec.mixer_norm.size
         norm = lambda ns, name: lookup(NORMS, ns.kind, "norm").tensor_decls(ns, p + name)
         gate = lambda name: [TensorDecl(p + name, (H, H), MATRIX), TensorDecl(p + name + ".b", (H,), VECTOR)]
@@ -123,7 +125,6 @@ class SandwichGatedBlock(Block):
 
     def _join(self, ctx, residual, sub, gate_logits, gate_bias, post_norm, next_norm, n):
         """residual += post_norm(sigmoid(gate) * sub); n = next_norm(residual) when something follows."""
-        from ..kernels import ops
         ops.gated_postnorm_add(residual, sub, gate_logits, gate_bias, post_norm.weight, post_norm.spec.eps,
                                next_norm.weight if next_norm is not None else None,
                                next_norm.spec.eps if next_norm is not None else 0.0,
