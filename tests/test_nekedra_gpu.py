@@ -453,3 +453,52 @@ def test_command_line_and_trace_replay(tmp_path, tmp_path_factory):
         biggest = max(np.abs(ra).max(), np.abs(rb).max())
         for got, ref in ((read(0), ra[[0, 29]]), (read(1), ra[[31]]), (read(2), np.stack([rb[39], ra[49]]))):
             assert got.shape == ref.shape and np.abs(got - ref).max() <= TOL[dtype] * biggest
+
+
+# ---- configurations drawn at random: layer order, sizes and constants that no other test chose -----------------
+
+def random_config(seed):
+    rng = np.random.default_rng(1000 + seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]
+    width = pick(32, 48, 64, 96, 128)
+    layers, mixes = [], None
+    for _ in range(int(rng.integers(3, 7))):
+        kind = pick("attention", "latent_attention", "delta")
+        ff = pick(0, 40, 72, 128)
+        if kind == "attention":
+            kv = pick(1, 2, 3)
+            v_mix = pick(True, False, None)
+            dim, vdim = pick(8, 16, 24, 32, 64), pick(8, 16, 40, 64, 128)
+            if v_mix:                                   # layers that mix share the size of their values
+                if mixes is None:
+                    mixes = (kv, vdim)
+                kv, vdim = mixes
+            layers.append(attention(heads=kv * pick(1, 2, 4), kv_heads=kv, dim=dim, vdim=vdim, v_mix=v_mix, ff=ff))
+            layers[-1]["mixer"]["scale"] = float(pick(0.1, 0.25, dim ** -0.5))
+        elif kind == "latent_attention":
+            rot_dim = pick(4, 8, 16, 32)
+            layers.append(latent(heads=pick(1, 2, 3, 5, 8), dim=pick(8, 16, 32, 48), rot_dim=rot_dim,
+                                 dims=pick(rot_dim, rot_dim, max(2, rot_dim // 2)), rank=pick(16, 24, 64, 128),
+                                 vdim=pick(8, 16, 64), base=float(pick(100.0, 10000.0, 500000.0)), ff=ff))
+        else:
+            kv = pick(1, 2, 3)
+            layers.append(delta(heads=kv * pick(1, 2, 3), kv_heads=kv, dim=pick(8, 16, 32, 72), vdim=pick(8, 16, 24, 64),
+                                conv=pick(1, 2, 3, 4, 5), ff=ff))
+    return config(layers, width=width, vocab=int(rng.integers(50, 400)), eps=float(pick(1e-6, 1e-5, 1e-4)))
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_configurations_drawn_at_random(seed, dtype, tmp_path_factory):
+    name = f"random{seed}"
+    CONFIGS.setdefault(name, random_config(seed))
+    model = (name,) + folder_of(name, tmp_path_factory)
+    cfg = model[2]
+    rng = np.random.default_rng(seed)
+    reqs = {k: random_tokens(rng, n, cfg["vocab"]) for k, n in (("a", 90), ("b", 37), ("c", 5))}
+    eng = build(model[1], dtype, num_pages=32, page_size=8)
+    got = replay(eng, cut_bulk_tail("a", reqs["a"], 30))
+    got.update(replay(eng, cut_portions("b", reqs["b"])))
+    got.update(replay(eng, cut_whole("c", reqs["c"])))
+    check(got, model, reqs, dtype)
+    assert all_pages_free(eng, 32)
