@@ -159,7 +159,9 @@ def check(got, model, requests, dtype):
         assert far.size == 0 and bad.size <= allowed, (
             f"{name} request {rid}: first wrong position {bad[0]} of {len(tokens)} "
             f"(rel err {err[bad[0]]:.3e} > {tol:.1e}); wrong positions {bad[:20]}")
-        note_error(dtype, float(err.max()), "nekedra " + name)
+        label = dtype if dtype == "float32" else ("bfloat16, Nekedra: the tolerance grows with the root of the depth, and one "
+                                                  "position in fifty may reach three times it")
+        note_error(label, float(err.max()), "nekedra " + name)
 
 
 def all_pages_free(eng, n):
