@@ -159,12 +159,76 @@ class DeltaRuleSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class DistanceAttentionNames:
+    """Tensor names of an attention mixer with a distance penalty, each appended to its layer's ``weight_prefix``."""
+    q: str = "mix.q"
+    k: str = "mix.k"
+    v: str = "mix.v"
+    o: str = "mix.o"
+    gate: str = "mix.g"                     # [heads, hidden]: one gate logit per head
+    temperature: str = "mix.temp"           # [heads]
+    penalty_weight: str = "mix.r1"          # [heads]
+    penalty_rate: str = "mix.r2"            # [heads]
+
+
+@dataclass(frozen=True)
+class DistanceAttentionSpec(MixerSpec):
+    """Grouped-query attention without a rotation, whose scores fall with the distance to the key:
+
+        score(i, j) = (q_i . k_j) * softmax_scale * temperature_h - weight_h * ln(1 + rate_h * (i - j))
+
+    over the keys 0 <= i - j < window (all earlier keys when window is None); q and k are divided by their
+    root mean square per head when ``unit_norm_eps`` is given; a head's output is multiplied by the
+    logistic of a per-head projection of the mixer's input when ``output_gate`` is set."""
+    hidden_size: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0                       # query / key size
+    v_head_dim: int = 0                     # value size
+    softmax_scale: float = 0.0
+    window: Optional[int] = None
+    unit_norm_eps: Optional[float] = None   # None: q and k as projected
+    temperature: bool = True                # a learned factor per head on the scores
+    distance_penalty: bool = True           # the logarithmic penalty above, two learned numbers per head
+    output_gate: bool = True
+    names: DistanceAttentionNames = DistanceAttentionNames()
+
+
+@dataclass(frozen=True)
 class FeedForwardSpec:
     kind: str            # registry key in parts.FEED_FORWARDS
     hidden_size: int
     intermediate_size: int
     activation: str = "silu"
     names: GatedDenseNames = GatedDenseNames()   # read by the gated dense part; other kinds name their own
+
+
+@dataclass(frozen=True)
+class RoutedExpertsNames:
+    """Tensor names of a routed feed-forward; expert e's tensors start with ``expert.format(e)``."""
+    router: str = "mlp.router"
+    router_bias: str = "mlp.router.b"
+    expert: str = "mlp.e{}."
+    shared: str = "mlp.shared."
+    gate: str = "gate"
+    up: str = "up"
+    down: str = "down"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec(FeedForwardSpec):
+    """``experts`` small gated feed-forwards of which every token uses the ``top`` with the largest router
+    logits, weighted by the softmax over those logits alone; plus, optionally, one that every token uses.
+    ``activation`` "clamped_glu": y = g * logistic(glu_alpha * g) * (u + 1) with g = min(gate, limit),
+    u = clamp(up, -limit, limit).  intermediate_size is one expert's."""
+    experts: int = 0
+    top: int = 0
+    limit: float = 0.0
+    glu_alpha: float = 1.702
+    router_bias: bool = True
+    shared_size: int = 0                    # 0: no expert that every token uses
+    shared_limit: float = 0.0
+    expert_names: RoutedExpertsNames = RoutedExpertsNames()
 
 
 @dataclass(frozen=True)
@@ -210,6 +274,9 @@ class ModelSpec:
     head_name: str = "lm_head.weight"
     embed_position: Optional[PositionSpec] = None   # an encoding that adds to the embedded tokens (none in Qwen3)
     embed_position_name: str = "model.embed_positions.weight"
+    embed_norm: Optional[NormSpec] = None           # a norm of the embedded tokens before the first layer
+    embed_norm_name: str = "embed.norm"
+    logit_softcap: Optional[float] = None           # logits <- cap * tanh(logits / cap)
     extra: dict = field(default_factory=dict, compare=False)
 
     def to_json(self) -> dict:

@@ -5,7 +5,9 @@
 //     first dv elements of the keys (a cache that holds one latent vector per token serves as both);
 //   * an optional sink per query head: one more term exp(sink) in the softmax denominator, with no
 //     key and no value behind it;
-//   * queries are float32 (they may be the product of a projection folded into them).
+//   * queries are float32 (they may be the product of a projection folded into them);
+//   * optional per-head changes to the scores (ScoreMods in common.cuh): a learned factor, and a penalty
+//     that grows with the logarithm of the distance between query and key.
 //
 // A block takes 16 rows (tokens x query heads of one KV head) of one entry and walks the keys in
 // blocks of 32 aligned to the start of the sequence; a row's sums depend on its position alone (key
@@ -29,7 +31,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
                                const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
                                const int* __restrict__ kv_lens, const float* __restrict__ sinks, int nq, int nkv,
                                int dk, int dv, int page_size, float scale, int window, int nsplit, int kv_chunk,
-                               float* __restrict__ part_o, float* __restrict__ part_ml) {
+                               float* __restrict__ part_o, float* __restrict__ part_ml, ScoreMods mods) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   extern __shared__ float smem[];
@@ -58,7 +60,9 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
   }
 
   float m[kRowsPerWarp], l[kRowsPerWarp], acc[kRowsPerWarp][VPL];
+  float row_scale[kRowsPerWarp], pen_w[kRowsPerWarp], pen_r[kRowsPerWarp];
   int pos[kRowsPerWarp], first[kRowsPerWarp];
+  const bool penalised = mods.pen_weight != nullptr;
 #pragma unroll
   for (int i = 0; i < kRowsPerWarp; ++i) {
     const int row = r0 + warp * kRowsPerWarp + i;
@@ -66,6 +70,9 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
     pos[i] = live ? start + row / G : -1;                  // a row beyond the entry sees no key
     first[i] = (window > 0 && live) ? max(0, pos[i] - window + 1) : 0;
     const int h = kvh * G + (live ? row % G : 0);
+    row_scale[i] = mods.head_scale ? scale * mods.head_scale[h] : scale;
+    pen_w[i] = penalised ? mods.pen_weight[h] : 0.f;
+    pen_r[i] = penalised ? mods.pen_rate[h] : 0.f;
     const bool with_sink = sinks && (!sliced || blockIdx.x == 0);     // the sink counts once
     m[i] = with_sink ? sinks[h] : -CUDART_INF_F;
     l[i] = with_sink ? 1.f : 0.f;
@@ -86,7 +93,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
     for (int idx = tid; idx < kKeys * dk; idx += blockDim.x) {
       const int jj = idx / dk, d = idx - jj * dk, j = jb + jj;
       float v = 0.f;
-      if (j <= last_key) {
+      if (j >= first_key && j <= last_key) {               // pages before a window's first key may be given back
         const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
         v = to_float(k_cache[rowi * dk + d]);
       }
@@ -96,7 +103,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
       for (int idx = tid; idx < kKeys * dv; idx += blockDim.x) {
         const int jj = idx / dv, d = idx - jj * dv, j = jb + jj;
         float v = 0.f;
-        if (j <= last_key) {
+        if (j >= first_key && j <= last_key) {               // pages before a window's first key may be given back
           const size_t rowi = ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size);
           v = to_float(v_cache[rowi * dv + d]);
         }
@@ -119,7 +126,11 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
 #pragma unroll
     for (int i = 0; i < kRowsPerWarp; ++i) {
       const bool valid = j <= pos[i] && j >= first[i];
-      const float s = valid ? dot[i] * scale : -CUDART_INF_F;
+      float s = -CUDART_INF_F;
+      if (valid) {
+        s = dot[i] * row_scale[i];
+        if (penalised) s -= distance_penalty(pen_w[i], pen_r[i], pos[i] - j);
+      }
       const float m_new = fmaxf(m[i], warp_max(s));
       float alpha = 1.f, p = 0.f;
       if (m_new != -CUDART_INF_F) {                        // else: nothing seen yet, nothing to rescale
@@ -258,19 +269,68 @@ __global__ void attention_bias_append_kernel(const TP* __restrict__ proj, long l
   }
 }
 
+// One block per token: every q head and every k head of a stacked q | k | v projection is divided by
+// its root mean square, sqrt(mean(x^2) + eps), in float32 (eps <= 0: left as projected); q goes to its
+// own buffer (float32, or bfloat16 for the kernels that take their queries so), k and v to the pages.
+// A warp takes a head at a time and adds the squares in an order fixed by the head size.
+template <typename TP, typename TC>
+__global__ void attention_unit_norm_append_kernel(const TP* __restrict__ proj, long long ldp, float eps,
+                                                  float* __restrict__ q_out, bf16* __restrict__ q_out_bf16,
+                                                  TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+                                                  const int* __restrict__ kv_slot, int write_kv, int nq, int nkv,
+                                                  int dk, int dv, int page_size) {
+  pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const TP* p = proj + (size_t)t * ldp;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int slot = kv_slot[t];
+  const size_t page = slot / page_size, off = slot % page_size;
+  for (int h = warp; h < nq + nkv; h += warps) {
+    const bool is_q = h < nq;
+    if (!is_q && !write_kv) continue;
+    const TP* x = p + (size_t)h * dk;                       // the k heads follow the q heads, all dk wide
+    float inv = 1.f;
+    if (eps > 0.f) {
+      float ss = 0.f;
+      for (int d = lane; d < dk; d += 32) {
+        const float v = to_float(x[d]);
+        ss += v * v;
+      }
+      inv = 1.f / sqrtf(warp_sum(ss) / (float)dk + eps);
+    }
+    for (int d = lane; d < dk; d += 32) {
+      const float v = to_float(x[d]) * inv;
+      if (is_q) {
+        if (q_out_bf16) q_out_bf16[((size_t)t * nq + h) * dk + d] = __float2bfloat16_rn(v);
+        else q_out[((size_t)t * nq + h) * dk + d] = v;
+      } else {
+        k_cache[((page * nkv + (h - nq)) * page_size + off) * dk + d] = from_float<TC>(v);
+      }
+    }
+  }
+  if (write_kv) {
+    const TP* v_in = p + (size_t)(nq + nkv) * dk;
+    for (int c = threadIdx.x; c < nkv * dv; c += blockDim.x) {
+      const int h = c / dv, d = c - h * dv;
+      v_cache[((page * nkv + h) * page_size + off) * dv + d] = from_float<TC>(to_float(v_in[c]));
+    }
+  }
+}
+
 template <typename TC, typename TO>
 static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, const float* q, const void* k_cache,
                           const void* v_cache, void* out, const int* block_table, int table_stride, const int* cu_q,
                           const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
                           float scale, int window, int nsplit, int kv_chunk, float* part_o, float* part_ml,
-                          int n_entries) {
+                          int n_entries, ScoreMods mods) {
 #define SRLM_GENERAL_CASE(V)                                                                                   \
   case V: {                                                                                                    \
     auto kern = paged_attention_general_kernel<TC, TO, V>;                                                     \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     launch_pdl(kern, dim3(grid), dim3(kWarps * 32), smem, stream, q, (const TC*)k_cache, (const TC*)v_cache, (TO*)out, block_table, \
                                               table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size,  \
-                                              scale, window, nsplit, kv_chunk, part_o, part_ml);               \
+                                              scale, window, nsplit, kv_chunk, part_o, part_ml, mods);         \
     break;                                                                                                     \
   }
   switch (vpl) {
@@ -300,8 +360,12 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
                                             int table_stride, const int* cu_q, const int* kv_lens,
                                             const float* sinks, int n_entries, int max_q_len, int nq, int nkv,
                                             int dk, int dv, int page_size, float scale, int window, int nsplit,
-                                            int kv_chunk, float* part_o, float* part_ml, cudaStream_t stream) {
+                                            int kv_chunk, float* part_o, float* part_ml, const float* head_scale,
+                                            const float* pen_weight, const float* pen_rate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  if ((pen_weight == nullptr) != (pen_rate == nullptr))
+    return refuse(ST_BAD_SIZE, "paged_attention_general: a distance penalty needs its weight and its rate");
+  const ScoreMods mods{head_scale, pen_weight, pen_rate};
   if (nq <= 0 || nkv <= 0 || nq % nkv || dk <= 0 || dv <= 0 || dv > 512 || page_size <= 0 || (!v_cache && dv > dk))
     return refuse(ST_BAD_SIZE, "paged_attention_general: nq=%d nkv=%d dk=%d dv=%d page_size=%d (dv <= 512; values "
                   "read from the keys need dv <= dk)", nq, nkv, dk, dv, page_size);
@@ -322,15 +386,15 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
   if (cache_dtype == DT_F32 && out_dtype == DT_F32)
     return launch_general<float, float>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
                                         cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
-                                        part_o, part_ml, n_entries);
+                                        part_o, part_ml, n_entries, mods);
   if (cache_dtype == DT_BF16 && out_dtype == DT_F32)
     return launch_general<bf16, float>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
                                        cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
-                                        part_o, part_ml, n_entries);
+                                        part_o, part_ml, n_entries, mods);
   if (cache_dtype == DT_BF16 && out_dtype == DT_BF16)
     return launch_general<bf16, bf16>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
                                       cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
-                                        part_o, part_ml, n_entries);
+                                        part_o, part_ml, n_entries, mods);
   return refuse(ST_BAD_DTYPE, "paged_attention_general: cache dtype %d with output dtype %d", cache_dtype, out_dtype);
 }
 
@@ -374,5 +438,26 @@ extern "C" int srlm_attention_general_merge(const float* part_o, const float* pa
                                                                        nkv, dv, nsplit, rows_padded);
   else
     return refuse(ST_BAD_DTYPE, "attention_general_merge: output dtype %d", out_dtype);
+  return launched();
+}
+
+// proj: [T, ldp] in proj_dtype, columns q (nq * dk), k (nkv * dk), v (nkv * dv), then whatever else the
+// projection carries.  q and k heads divided by sqrt(mean(x^2) + eps) (eps <= 0: not), q to q_out, k and v to the pages.
+extern "C" int srlm_attention_unit_norm_append(const void* proj, int proj_dtype, long long ldp, float eps, void* q_out,
+                                               int q_dtype, void* k_cache, void* v_cache, int cache_dtype,
+                                               const int* kv_slot, int write_kv, int T, int nq, int nkv, int dk, int dv,
+                                               int page_size, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (nq <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || page_size <= 0 || ldp < (long long)nq * dk + (long long)nkv * (dk + dv))
+    return refuse(ST_BAD_SIZE, "attention_unit_norm_append: nq=%d nkv=%d dk=%d dv=%d ldp=%lld", nq, nkv, dk, dv, ldp);
+#define SRLM_APPEND(TP, TC)                                                                                       \
+  launch_pdl(attention_unit_norm_append_kernel<TP, TC>, dim3(T), dim3(256), 0, stream, (const TP*)proj, ldp, eps, \
+             q_dtype == DT_F32 ? (float*)q_out : nullptr, q_dtype == DT_BF16 ? (bf16*)q_out : nullptr,            \
+             (TC*)k_cache, (TC*)v_cache, kv_slot, write_kv, nq, nkv, dk, dv, page_size)
+  if (proj_dtype == DT_F32 && cache_dtype == DT_F32) SRLM_APPEND(float, float);
+  else if (proj_dtype == DT_F32 && cache_dtype == DT_BF16) SRLM_APPEND(float, bf16);
+  else if (proj_dtype == DT_BF16 && cache_dtype == DT_BF16) SRLM_APPEND(bf16, bf16);
+  else return refuse(ST_BAD_DTYPE, "attention_unit_norm_append: projection dtype %d with cache dtype %d", proj_dtype, cache_dtype);
+#undef SRLM_APPEND
   return launched();
 }

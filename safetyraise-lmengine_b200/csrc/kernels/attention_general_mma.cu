@@ -53,7 +53,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
                                    const float* __restrict__ sinks, int nq, int nkv, int dk, int dv, int page_size,
                                    float scale, int window, int nbuf, const bf16* __restrict__ kv_rows,
                                    long long ld_rows, const int* __restrict__ cu_kv, int dim_rows, int v_off,
-                                   int page_skip) {
+                                   int page_skip, ScoreMods mods) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   // kv_rows != null: every query head has keys and values of its own (nkv = nq), formed for this step in
@@ -89,8 +89,9 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   }
 
   // a thread's two rows of its warp's 16: lane / 4 and lane / 4 + 8
-  float m[2], l[2];
+  float m[2], l[2], row_scale[2], pen_w[2], pen_r[2];
   int pos[2], first[2];
+  const bool penalised = mods.pen_weight != nullptr;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = r0 + warp * 16 + (lane >> 2) + 8 * i;
@@ -98,6 +99,9 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
     pos[i] = live ? start + row / G : -1;
     first[i] = (window > 0 && live) ? max(0, pos[i] - window + 1) : 0;
     const int h = kvh * G + (live ? row % G : 0);
+    row_scale[i] = mods.head_scale ? scale * mods.head_scale[h] : scale;
+    pen_w[i] = penalised ? mods.pen_weight[h] : 0.f;
+    pen_r[i] = penalised ? mods.pen_rate[h] : 0.f;
     m[i] = sinks ? sinks[h] : -CUDART_INF_F;
     l[i] = sinks ? 1.f : 0.f;
   }
@@ -117,7 +121,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   auto fetch = [&](int jb, int buf) {
     for (int idx = tid; idx < kMmaKeys * kvec; idx += blockDim.x) {
       const int jj = idx / kvec, c = idx - jj * kvec, j = jb + jj;
-      const bool there = j <= max_pos;
+      const bool there = j >= first_key && j <= max_pos;     // pages before a window's first key may be given back
       const bf16* src = k_cache;
       if (there && kv_rows) {
         if (c * 8 < dim_rows) {
@@ -135,7 +139,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
     if (v_cache || kv_rows) {
       for (int idx = tid; idx < kMmaKeys * vvec; idx += blockDim.x) {
         const int jj = idx / vvec, c = idx - jj * vvec, j = jb + jj;
-        const bool there = j <= max_pos;
+        const bool there = j >= first_key && j <= max_pos;     // pages before a window's first key may be given back
         const bf16* src = k_cache;
         if (there && kv_rows) {
           src = kv_rows + (row0 + j) * ld_rows + v_off + (size_t)kvh * dv + slab * DVT + c * 8;
@@ -196,7 +200,11 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
         for (int c = 0; c < 2; ++c) {
           const int j = jb + n * 8 + (lane & 3) * 2 + c;
           const bool valid = j <= pos[i] && j >= first[i];
-          const float v = valid ? s[n][2 * i + c] * scale : -CUDART_INF_F;
+          float v = -CUDART_INF_F;
+          if (valid) {
+            v = s[n][2 * i + c] * row_scale[i];
+            if (penalised) v -= distance_penalty(pen_w[i], pen_r[i], pos[i] - j);
+          }
           s[n][2 * i + c] = v;
           mx = fmaxf(mx, v);
         }
@@ -284,7 +292,8 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
                                       const int* __restrict__ cu_q, const int* __restrict__ kv_lens,
                                       const float* __restrict__ sinks, int nq, int nkv, int dk, int dv,
                                       int page_size, float scale, int window, int nsplit, int kv_chunk,
-                                      float* __restrict__ part_o, float* __restrict__ part_ml, int row_tiles) {
+                                      float* __restrict__ part_o, float* __restrict__ part_ml, int row_tiles,
+                                      ScoreMods mods) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -308,14 +317,19 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
     const float v = row < rows ? q[((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dk + d] : 0.f;
     q_s[r * ks + d] = __float2bfloat16_rn(v);
   }
-  float m[2], l[2];
+  float m[2], l[2], row_scale[2], pen_w[2], pen_r[2];
   int pos[2], first[2];
+  const bool penalised = mods.pen_weight != nullptr;
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = r0 + (lane >> 2) + 8 * i;
     const bool live = row < rows;
     pos[i] = live ? start + row / G : -1;
     first[i] = (window > 0 && live) ? max(0, pos[i] - window + 1) : 0;
+    const int h = kvh * G + (live ? row % G : 0);
+    row_scale[i] = mods.head_scale ? scale * mods.head_scale[h] : scale;
+    pen_w[i] = penalised ? mods.pen_weight[h] : 0.f;
+    pen_r[i] = penalised ? mods.pen_rate[h] : 0.f;
     const bool with_sink = sinks && slice == 0;             // the sink counts once
     m[i] = with_sink ? sinks[kvh * G + (live ? row % G : 0)] : -CUDART_INF_F;
     l[i] = with_sink ? 1.f : 0.f;
@@ -338,14 +352,14 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
   auto fetch = [&](int jb, int buf) {
     for (int idx = tid; idx < kDecKeys * kvec; idx += blockDim.x) {
       const int jj = idx / kvec, c = idx - jj * kvec, j = jb + jj;
-      const bool there = j <= last_key;
+      const bool there = j >= first_key && j <= last_key;
       const size_t rowi = there ? ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size) : 0;
       cp_async_16(k_s + buf * k_tile + jj * ks + c * 8, k_cache + rowi * dk + c * 8, there);
     }
     if (v_cache) {
       for (int idx = tid; idx < kDecKeys * vvec; idx += blockDim.x) {
         const int jj = idx / vvec, c = idx - jj * vvec, j = jb + jj;
-        const bool there = j <= last_key;
+        const bool there = j >= first_key && j <= last_key;
         const size_t rowi = there ? ((size_t)table[j / page_size] * nkv + kvh) * page_size + (j % page_size) : 0;
         cp_async_16(v_s + buf * v_tile + jj * vs + c * 8, v_cache + rowi * dv + c * 8, there);
       }
@@ -390,7 +404,11 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
         for (int c = 0; c < 2; ++c) {
           const int j = jb + n * 8 + (lane & 3) * 2 + c;
           const bool valid = j <= pos[i] && j >= first[i] && j >= first_key && j <= last_key;
-          const float v = valid ? s[n][2 * i + c] * scale : -CUDART_INF_F;
+          float v = -CUDART_INF_F;
+          if (valid) {
+            v = s[n][2 * i + c] * row_scale[i];
+            if (penalised) v -= distance_penalty(pen_w[i], pen_r[i], pos[i] - j);
+          }
           s[n][2 * i + c] = v;
           mx = fmaxf(mx, v);
         }
@@ -474,12 +492,13 @@ static int launch_mma(dim3 grid, size_t smem, cudaStream_t stream, const float* 
                       const void* v_cache, void* out, const int* block_table, int table_stride, const int* cu_q,
                       const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
                       float scale, int window, int nbuf, const bf16* kv_rows = nullptr, long long ld_rows = 0,
-                      const int* cu_kv = nullptr, int dim_rows = 0, int v_off = 0, int page_skip = 0) {
+                      const int* cu_kv = nullptr, int dim_rows = 0, int v_off = 0, int page_skip = 0,
+                      ScoreMods mods = ScoreMods{nullptr, nullptr, nullptr}) {
   auto kern = paged_attention_general_mma_kernel<TO, NT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   launch_pdl(kern, dim3(grid), dim3(kMmaWarps * 32), smem, stream, q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out, block_table,
                                                table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale,
-                                               window, nbuf, kv_rows, ld_rows, cu_kv, dim_rows, v_off, page_skip);
+                                               window, nbuf, kv_rows, ld_rows, cu_kv, dim_rows, v_off, page_skip, mods);
   return launched();
 }
 
@@ -501,8 +520,12 @@ extern "C" int srlm_paged_attention_general_mma(const float* q, const void* k_ca
                                                 int out_dtype, const int* block_table, int table_stride,
                                                 const int* cu_q, const int* kv_lens, const float* sinks,
                                                 int n_entries, int max_q_len, int nq, int nkv, int dk, int dv,
-                                                int page_size, float scale, int window, cudaStream_t stream) {
+                                                int page_size, float scale, int window, const float* head_scale,
+                                                const float* pen_weight, const float* pen_rate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  if ((pen_weight == nullptr) != (pen_rate == nullptr))
+    return refuse(ST_BAD_SIZE, "paged_attention_general_mma: a distance penalty needs its weight and its rate");
+  const ScoreMods mods{head_scale, pen_weight, pen_rate};
   if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || !srlm_attention_general_mma_takes(dk, dv, v_cache ? 0 : 1))
     return refuse(ST_BAD_SIZE, "paged_attention_general_mma: nq=%d nkv=%d dk=%d dv=%d page_size=%d (dk a multiple of "
                   "16, dv of 64)", nq, nkv, dk, dv, page_size);
@@ -520,7 +543,7 @@ extern "C" int srlm_paged_attention_general_mma(const float* q, const void* k_ca
   const int nbuf = q_bytes + 2 * tile_bytes <= 100 * 1024 ? 2 : 1;
   const size_t smem = q_bytes + nbuf * tile_bytes;
 #define SRLM_MMA_ARGS grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_lens, sinks, nq, \
-                      nkv, dk, dv, page_size, scale, window, nbuf
+                      nkv, dk, dv, page_size, scale, window, nbuf, nullptr, 0, nullptr, 0, 0, 0, mods
   if (out_dtype == DT_F32) return slab == 128 ? launch_mma<float, 16>(SRLM_MMA_ARGS) : launch_mma<float, 8>(SRLM_MMA_ARGS);
   if (out_dtype == DT_BF16) return slab == 128 ? launch_mma<bf16, 16>(SRLM_MMA_ARGS) : launch_mma<bf16, 8>(SRLM_MMA_ARGS);
 #undef SRLM_MMA_ARGS
@@ -540,8 +563,12 @@ extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k
                                                    const int* cu_q, const int* kv_lens, const float* sinks,
                                                    int n_entries, int max_q_len, int nq, int nkv, int dk, int dv,
                                                    int page_size, float scale, int window, int nsplit, int kv_chunk,
-                                                   float* part_o, float* part_ml, cudaStream_t stream) {
+                                                   float* part_o, float* part_ml, const float* head_scale,
+                                                   const float* pen_weight, const float* pen_rate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  if ((pen_weight == nullptr) != (pen_rate == nullptr))
+    return refuse(ST_BAD_SIZE, "paged_attention_general_decode: a distance penalty needs its weight and its rate");
+  const ScoreMods mods{head_scale, pen_weight, pen_rate};
   if (nq <= 0 || nkv <= 0 || nq % nkv || page_size <= 0 || !srlm_attention_general_decode_takes(dk, dv, v_cache ? 0 : 1))
     return refuse(ST_BAD_SIZE, "paged_attention_general_decode: nq=%d nkv=%d dk=%d dv=%d rows=%d", nq, nkv, dk, dv,
                   max_q_len * (nq / (nkv > 0 ? nkv : 1)));
@@ -562,7 +589,7 @@ extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k
     launch_pdl(kern, dim3(grid), dim3(kMmaWarps * 32), smem, stream, q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out,          \
                                                  block_table, table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, \
                                                  page_size, scale, window, nsplit, kv_chunk, part_o, part_ml,      \
-                                                 row_tiles);                                                       \
+                                                 row_tiles, mods);                                                 \
   } while (0)
 #define SRLM_DEC_SIZES(TO)                                \
   do {                                                    \

@@ -67,6 +67,18 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Optional changes to an attention score, per query head (each pointer float32 [query heads] or null):
+//   score = (q . k) * scale * head_scale[h] - pen_weight[h] * ln(1 + pen_rate[h] * (i - j))
+// for query position i and key position j.  pen_weight and pen_rate come together.
+struct ScoreMods {
+  const float* head_scale;
+  const float* pen_weight;
+  const float* pen_rate;
+};
+__device__ __forceinline__ float distance_penalty(float weight, float rate, int distance) {
+  return weight * log1pf(rate * (float)distance);
+}
+
 // Sum over a block in a fixed order (depends on blockDim only).  scratch: 32 floats.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

@@ -174,6 +174,14 @@ __global__ void check_finite_kernel(const float* __restrict__ a, const TB* __res
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicExch(flag, 1);
 }
 
+// x <- cap * tanh(x / cap), in place
+__global__ void softcap_kernel(float* __restrict__ x, float cap, size_t n) {
+  pdl_wait();
+  pdl_trigger();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] / cap);
+}
+
 static inline int norm_block(int H) {
   int b = 32;
   while (b < 1024 && b * 4 < H) b <<= 1;
@@ -279,5 +287,13 @@ extern "C" int srlm_check_finite(const float* a, const void* b, int b_dtype, lon
   const int grid = flat_grid((size_t)n, 256);
   SRLM_DISPATCH_ACT(b_dtype, TB, launch_pdl(check_finite_kernel<TB>, dim3(grid), dim3(256), 0, stream,
       a, (const TB*)b, (size_t)n, flag));
+  return launched();
+}
+
+// Logits bounded by a smooth cap: x <- cap * tanh(x / cap), float32 in place.
+extern "C" int srlm_softcap(float* x, float cap, long long n, cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  if (!(cap > 0.f)) return refuse(ST_BAD_SIZE, "softcap: cap=%g", (double)cap);
+  launch_pdl(softcap_kernel, dim3(flat_grid((size_t)n, 256)), dim3(256), 0, stream, x, cap, (size_t)n);
   return launched();
 }

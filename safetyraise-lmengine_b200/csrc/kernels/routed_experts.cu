@@ -1,0 +1,344 @@
+// A feed-forward of routed experts: every token runs the `top` experts with the largest router logits and
+// adds their outputs, weighted by the softmax over those logits alone.
+//
+//   route    router logits (+ bias) -> the chosen experts and their weights, per token (float32)
+//   sort     the (token, choice) pairs ordered by expert: where each expert's rows start, which pair
+//            sits in which row, and how many tiles of kTile rows each expert has
+//   grouped  C[row] = A[row's token] . W[row's expert]^T for all experts in one launch; with the gated
+//            activation in its epilogue for the experts' first product
+//   combine  out[token] = sum over its choices, in the order of the choices, of weight * row (+ the
+//            output of the expert that every token runs)
+//
+// Nothing here depends on what else is in the batch: a row's sums run over k in index order whatever
+// tile the row landed in, and the combination adds a token's rows in the order of its choices.
+// Everything is sized on the host by upper bounds (pairs / kTile + experts tiles), so a step's launches
+// depend on its token count alone and can be replayed from a CUDA graph.
+//
+// The gated activation of an expert ("clamped GLU"): g = min(gate, limit), u = clamp(up, -limit, limit),
+// y = g * logistic(alpha * g) * (u + 1).
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace srlm {
+
+constexpr int kTile = 64;        // rows (token, choice pairs) of a tile of the grouped products
+
+__device__ __forceinline__ float clamped_glu(float gate, float up, float limit, float alpha) {
+  const float g = fminf(gate, limit);
+  const float u = fminf(fmaxf(up, -limit), limit);
+  return g * (1.f / (1.f + expf(-alpha * g))) * (u + 1.f);
+}
+
+// One warp per token.  The row of logits sits in shared memory; `top` times the warp takes the largest
+// value left (ties: the lowest index) and strikes it out.  weights = softmax over the chosen values.
+__global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ bias,
+                                 int T, int E, int top, int* __restrict__ choice, float* __restrict__ weight) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ float route_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int t = blockIdx.x * warps + warp;
+  if (t >= T) return;
+  float* z = route_smem + (size_t)warp * E;
+  for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)t * ld + e] + (bias ? bias[e] : 0.f);
+  __syncwarp();
+  float first = 0.f, sum = 0.f;
+  for (int c = 0; c < top; ++c) {
+    float best = -CUDART_INF_F;
+    int at = E;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }     // NaN never wins: a struck-out slot is -inf
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at >= E) at = c < E ? c : 0;            // a row of NaN: any valid expert; the step's finite check reports it
+    if (c == 0) first = best;
+    const float p = expf(best - first);
+    sum += p;
+    if (lane == 0) {
+      choice[(size_t)t * top + c] = at;
+      weight[(size_t)t * top + c] = p;
+      z[at] = -CUDART_INF_F;
+    }
+    __syncwarp();
+  }
+  __syncwarp();
+  for (int c = lane; c < top; c += 32) weight[(size_t)t * top + c] /= sum;
+}
+
+// One block.  offsets[E + 1]: first row of each expert; tiles[E + 1]: first tile of each expert (tiles of
+// kTile rows, none shared by two experts); pair_of_row[n]; row_of_pair[n].  Which row of its expert a pair
+// gets depends on the order the threads arrive in; no result depends on it.
+__global__ void moe_sort_kernel(const int* __restrict__ choice, int n, int E, int* __restrict__ offsets,
+                                int* __restrict__ tiles, int* __restrict__ pair_of_row, int* __restrict__ row_of_pair) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ int sort_smem[];
+  int* count = sort_smem;            // [E]
+  int* start = count + E;            // [E + 1]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = choice[i];
+    if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int rows = 0, tl = 0;
+    for (int e = 0; e < E; ++e) {
+      start[e] = rows;
+      offsets[e] = rows;
+      tiles[e] = tl;
+      rows += count[e];
+      tl += (count[e] + kTile - 1) / kTile;
+    }
+    start[E] = rows;
+    offsets[E] = rows;
+    tiles[E] = tl;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;       // now the cursor of each expert
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = choice[i];
+    if (e < 0 || e >= E) { row_of_pair[i] = -1; continue; }
+    const int row = start[e] + atomicAdd(&count[e], 1);
+    pair_of_row[row] = i;
+    row_of_pair[i] = row;
+  }
+}
+
+// The expert and the first row of tile `tile`; false when the step has fewer tiles.
+__device__ __forceinline__ bool tile_home(const int* __restrict__ offsets, const int* __restrict__ tiles, int E, int tile,
+                                          int& expert, int& row0, int& row_end) {
+  if (tile >= tiles[E]) return false;
+  int lo = 0, hi = E - 1;                                   // the last expert whose first tile is <= tile
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (tiles[mid] <= tile) lo = mid; else hi = mid - 1;
+  }
+  expert = lo;
+  row0 = offsets[lo] + (tile - tiles[lo]) * kTile;
+  row_end = offsets[lo + 1];
+  return true;
+}
+
+// Float32 arithmetic (FMA), any sizes: the float32 path, and sizes the tensor-core form does not take.
+// GLU: W holds per expert the gate rows of all features, then the up rows (interleaved == 0), or blocks
+// of 16 rows, 8 gate rows then the 8 up rows of the same features (interleaved == 1); C gets the
+// activation, N features wide.  Else C[row, 0..N) = A . W[expert]^T, N weight rows per expert.
+constexpr int GBN = 64, GBK = 16;
+
+template <typename TA, typename TW, typename TO, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_grouped_simt_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ pair_of_row, int pairs_per_token,
+                        const TW* __restrict__ W, TO* __restrict__ C, long long ldc, const int* __restrict__ offsets,
+                        const int* __restrict__ tiles, int E, int N, int K, int interleaved, float limit, float alpha) {
+  pdl_wait();
+  pdl_trigger();
+  __shared__ float As[GBK][kTile + 4];
+  __shared__ float Ws[GBK][GBN + 4];
+  __shared__ float Us[GLU ? GBK : 1][GBN + 4];
+  __shared__ int a_row[kTile];
+  int expert, row0, row_end;
+  if (!tile_home(offsets, tiles, E, blockIdx.y, expert, row0, row_end)) return;
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * GBN;
+  if (tid < kTile) {
+    const int row = row0 + tid;
+    a_row[tid] = row < row_end ? (pair_of_row ? pair_of_row[row] / pairs_per_token : row) : -1;
+  }
+  __syncthreads();
+  const size_t w_rows = GLU ? 2 * (size_t)N : (size_t)N;
+  const TW* We = W + (size_t)expert * w_rows * K;
+  const int tm = (tid / 16) * 4, tn = (tid % 16) * 4;
+  float acc[4][4] = {}, acu[GLU ? 4 : 1][4] = {};
+  for (int k0 = 0; k0 < K; k0 += GBK) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = tid + e * 256;
+      const int r = idx / GBK, c = idx % GBK;
+      const int k = k0 + c;
+      const int ar = a_row[r];
+      As[c][r] = (ar >= 0 && k < K) ? to_float(A[(size_t)ar * lda + k]) : 0.f;
+      const int f = n0 + r;
+      if (GLU) {
+        const size_t gr = interleaved ? (size_t)(f / 8) * 16 + f % 8 : (size_t)f;
+        const size_t ur = interleaved ? gr + 8 : (size_t)N + f;
+        Ws[c][r] = (f < N && k < K) ? to_float(We[gr * K + k]) : 0.f;
+        Us[c][r] = (f < N && k < K) ? to_float(We[ur * K + k]) : 0.f;
+      } else {
+        Ws[c][r] = (f < N && k < K) ? to_float(We[(size_t)f * K + k]) : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GBK; ++kk) {
+      float a[4], w[4], u[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = As[kk][tm + i];
+        w[i] = Ws[kk][tn + i];
+        if (GLU) u[i] = Us[kk][tn + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+          if (GLU) acu[GLU ? i : 0][j] = fmaf(a[i], u[j], acu[GLU ? i : 0][j]);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int row = row0 + tm + i;
+    if (row >= row_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tn + j;
+      if (n >= N) continue;
+      const float v = GLU ? clamped_glu(acc[i][j], acu[GLU ? i : 0][j], limit, alpha) : acc[i][j];
+      C[(size_t)row * ldc + n] = from_float<TO>(v);
+    }
+  }
+}
+
+// out[t, :] = sum_c weight[t, c] * rows[row_of_pair[t * top + c], :]  (+ shared[t, :]), float32 sums in the order of c
+template <typename TR, typename TA>
+__global__ void moe_combine_kernel(const TR* __restrict__ rows, long long ldr, const int* __restrict__ row_of_pair,
+                                   const float* __restrict__ weight, const TA* __restrict__ shared, TA* __restrict__ out,
+                                   int top, int H) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    float acc = 0.f;
+    for (int c = 0; c < top; ++c) {
+      const int row = row_of_pair[(size_t)t * top + c];
+      if (row >= 0) acc += weight[(size_t)t * top + c] * to_float(rows[(size_t)row * ldr + h]);
+    }
+    if (shared) acc += to_float(shared[(size_t)t * H + h]);
+    out[(size_t)t * H + h] = from_float<TA>(acc);
+  }
+}
+
+// in [T, 2 F]: gate in columns [0, F), up in [F, 2 F)  ->  out [T, F]
+template <typename TI, typename TA>
+__global__ void clamped_glu_kernel(const TI* __restrict__ in, TA* __restrict__ out, int F, size_t total, float limit,
+                                   float alpha) {
+  pdl_wait();
+  pdl_trigger();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / F, f = idx - t * F;
+    out[idx] = from_float<TA>(clamped_glu(to_float(in[t * 2 * F + f]), to_float(in[t * 2 * F + F + f]), limit, alpha));
+  }
+}
+
+}  // namespace srlm
+
+using namespace srlm;
+
+extern "C" int srlm_moe_tile_rows() { return kTile; }
+
+// logits float32 [T, ld >= E]; bias float32 [E] or null; choice int32 [T, top]; weight float32 [T, top]
+extern "C" int srlm_moe_route(const float* logits, long long ld, const float* bias, int T, int E, int top, int* choice,
+                              float* weight, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (E <= 0 || top <= 0 || top > E || ld < E || E > 8192)
+    return refuse(ST_BAD_SIZE, "moe_route: experts=%d top=%d ld=%lld (at most 8192 experts)", E, top, ld);
+  int warps = 4;
+  while (warps > 1 && (size_t)warps * E * sizeof(float) > 40 * 1024) warps >>= 1;
+  launch_pdl(moe_route_kernel, dim3((T + warps - 1) / warps), dim3(warps * 32), (size_t)warps * E * sizeof(float), stream,
+             logits, ld, bias, T, E, top, choice, weight);
+  return launched();
+}
+
+// choice int32 [n] (n = tokens x top); offsets, tiles int32 [E + 1]; pair_of_row, row_of_pair int32 [n]
+extern "C" int srlm_moe_sort(const int* choice, int n, int E, int* offsets, int* tiles, int* pair_of_row,
+                             int* row_of_pair, cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  if (E <= 0 || E > 4096) return refuse(ST_BAD_SIZE, "moe_sort: experts=%d (at most 4096)", E);
+  launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, choice, n, E, offsets, tiles,
+             pair_of_row, row_of_pair);
+  return launched();
+}
+
+// The most tiles a step of n pairs over E experts can have.
+static inline int tile_bound(int n, int E) {
+  const long long by_rows = (long long)n / kTile + E;      // each expert wastes less than one tile
+  return (int)(by_rows < n ? by_rows : n);
+}
+
+// glu != 0: W [E, 2 N, K], C [n, N] = the experts' activation; else W [E, N, K], C [n, N] = the product.
+// pair_of_row null: row r of A is row r of C (the experts' second product); else A's row is the pair's token.
+extern "C" int srlm_moe_grouped_simt(const void* A, int a_dtype, long long lda, const int* pair_of_row, int pairs_per_token,
+                                     const void* W, int w_dtype, void* C, int c_dtype, long long ldc, const int* offsets,
+                                     const int* tiles, int n, int E, int N, int K, int glu, int interleaved, float limit,
+                                     float alpha, cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  if (E <= 0 || N <= 0 || K <= 0 || lda < K || ldc < N || (pair_of_row && pairs_per_token <= 0) ||
+      (glu && interleaved && N % 8))
+    return refuse(ST_BAD_SIZE, "moe_grouped: experts=%d N=%d K=%d lda=%lld ldc=%lld", E, N, K, lda, ldc);
+  const int bound = tile_bound(n, E);
+  if (bound > 65535) return refuse(ST_BAD_SIZE, "moe_grouped: %d pairs over %d experts exceed 65535 tiles", n, E);
+  dim3 grid((N + GBN - 1) / GBN, bound);
+#define SRLM_GROUPED(TA, TW, TO)                                                                                      \
+  do {                                                                                                                \
+    if (glu) launch_pdl(moe_grouped_simt_kernel<TA, TW, TO, true>, grid, dim3(256), 0, stream, (const TA*)A, lda,    \
+                        pair_of_row, pairs_per_token, (const TW*)W, (TO*)C, ldc, offsets, tiles, E, N, K, interleaved, \
+                        limit, alpha);                                                                                \
+    else launch_pdl(moe_grouped_simt_kernel<TA, TW, TO, false>, grid, dim3(256), 0, stream, (const TA*)A, lda,       \
+                    pair_of_row, pairs_per_token, (const TW*)W, (TO*)C, ldc, offsets, tiles, E, N, K, interleaved,    \
+                    limit, alpha);                                                                                    \
+  } while (0)
+  if (a_dtype == DT_F32 && w_dtype == DT_F32 && c_dtype == DT_F32) SRLM_GROUPED(float, float, float);
+  else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && c_dtype == DT_BF16) SRLM_GROUPED(bf16, bf16, bf16);
+  else if (a_dtype == DT_BF16 && w_dtype == DT_BF16 && c_dtype == DT_F32) SRLM_GROUPED(bf16, bf16, float);
+  else return refuse(ST_BAD_DTYPE, "moe_grouped: dtypes (%d, %d) -> %d are not offered", a_dtype, w_dtype, c_dtype);
+#undef SRLM_GROUPED
+  return launched();
+}
+
+// rows [n, ldr] (float32 or the activation dtype); shared [T, H] in the activation dtype or null; out [T, H]
+extern "C" int srlm_moe_combine(const void* rows, int rows_dtype, long long ldr, const int* row_of_pair,
+                                const float* weight, const void* shared, void* out, int act_dtype, int T, int top, int H,
+                                cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (top <= 0 || H <= 0 || ldr < H) return refuse(ST_BAD_SIZE, "moe_combine: top=%d H=%d ldr=%lld", top, H, ldr);
+  int block = 32;
+  while (block < 256 && block < H) block <<= 1;
+#define SRLM_COMBINE(TR, TA)                                                                                   \
+  launch_pdl(moe_combine_kernel<TR, TA>, dim3(T), dim3(block), 0, stream, (const TR*)rows, ldr, row_of_pair,  \
+             weight, (const TA*)shared, (TA*)out, top, H)
+  if (rows_dtype == DT_F32 && act_dtype == DT_F32) SRLM_COMBINE(float, float);
+  else if (rows_dtype == DT_F32 && act_dtype == DT_BF16) SRLM_COMBINE(float, bf16);
+  else if (rows_dtype == DT_BF16 && act_dtype == DT_BF16) SRLM_COMBINE(bf16, bf16);
+  else return refuse(ST_BAD_DTYPE, "moe_combine: rows dtype %d with activation dtype %d", rows_dtype, act_dtype);
+#undef SRLM_COMBINE
+  return launched();
+}
+
+// in [T, 2 F] (float32 or the activation dtype): gate columns, then up columns; out [T, F]
+extern "C" int srlm_clamped_glu(const void* in, int in_dtype, void* out, int out_dtype, int T, int F, float limit,
+                                float alpha, cudaStream_t stream) {
+  if (T <= 0) return ST_OK;
+  if (F <= 0) return refuse(ST_BAD_SIZE, "clamped_glu: F=%d", F);
+  const size_t total = (size_t)T * F;
+  size_t g = (total + 255) / 256;
+  const int grid = (int)(g > 148 * 16 ? 148 * 16 : g);
+#define SRLM_GLU(TI, TA) launch_pdl(clamped_glu_kernel<TI, TA>, dim3(grid), dim3(256), 0, stream, (const TI*)in, (TA*)out, F, total, limit, alpha)
+  if (in_dtype == DT_F32 && out_dtype == DT_F32) SRLM_GLU(float, float);
+  else if (in_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_GLU(float, bf16);
+  else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_GLU(bf16, bf16);
+  else return refuse(ST_BAD_DTYPE, "clamped_glu: input dtype %d with output dtype %d", in_dtype, out_dtype);
+#undef SRLM_GLU
+  return launched();
+}

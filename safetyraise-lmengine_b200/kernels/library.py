@@ -777,11 +777,14 @@ class KernelLibrary:
     GENERAL_ROWS = 16        # rows (tokens x query heads of a KV head) of a block of the general attention kernel
 
     def paged_attention_general(self, ctx, q, k_cache, v_cache, out, block_table, sinks, nq, nkv, dk, dv, scale,
-                                window=0):
+                                window=0, head_scale=None, penalty=None):
         """Causal attention of the batch of ``ctx`` over pages whose keys have dk and whose values have dv
         elements (v_cache None: the values are the keys' first dv elements).  q float32 [T, nq * dk];
         k_cache [pages, nkv, page_size, dk]; out [T, nq * dv], float32 or the cache's dtype; sinks float32
-        [nq] or None: one more term exp(sink) in each head's softmax denominator.
+        [nq] or None: one more term exp(sink) in each head's softmax denominator.  head_scale float32 [nq] or
+        None: a factor per head on the scaled scores.  penalty (weight, rate), float32 [nq] each, or None:
+        weight * ln(1 + rate * distance to the key) is taken off the score.  window > 0: a query sees itself
+        and the window - 1 keys before it.
 
         A bfloat16 cache: the tensor-core forms (attention_general_mma.cu) when they take the sizes -- the
         decode form for steps of at most four tokens an entry (keys in slices, as many blocks as run at the
@@ -792,15 +795,16 @@ class KernelLibrary:
             raise ShapeError("paged_attention_general: float32 queries")
         n = ctx.n_entries
         g = nq // nkv
+        mods = (_ptr(head_scale), _ptr(penalty[0] if penalty else None), _ptr(penalty[1] if penalty else None))
         bf16 = k_cache.dtype == torch.bfloat16
         tensor_cores = bf16 and self.general_attention_on_tensor_cores
         from_keys = C.c_int(int(v_cache is None))
         # a decode step: one to four tokens an entry.  Its keys are cut into slices, as many blocks as run at once.
-        if (tensor_cores and ctx.max_q_len <= 4 and not window
+        if (tensor_cores and ctx.max_q_len <= 4
                 and self.lib.srlm_attention_general_decode_takes(C.c_int(dk), C.c_int(dv), from_keys)):
             rows_padded = (ctx.max_q_len * g + 15) // 16 * 16
             nsplit, chunk = self.attention_split(n, nkv * (rows_padded // 16), ctx.kv_bound, max_slices=64)
-            if not self.split_general_attention:
+            if not self.split_general_attention or window:      # a window's keys: one block walks them
                 nsplit, chunk = 1, 0
             part_o = part_ml = None
             if nsplit > 1:
@@ -813,7 +817,7 @@ class KernelLibrary:
                 C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks), C.c_int(n),
                 C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv), C.c_int(k_cache.shape[2]),
                 C.c_float(scale), C.c_int(window or 0), C.c_int(nsplit), C.c_int(chunk), _ptr(part_o), _ptr(part_ml),
-                _stream()), "paged_attention_general_decode")
+                *mods, _stream()), "paged_attention_general_decode")
             if nsplit > 1:
                 self._check(self.lib.srlm_attention_general_merge(
                     _ptr(part_o), _ptr(part_ml), _ptr(out), dtype_code(out.dtype), _ptr(ctx.cu_q), C.c_int(n),
@@ -828,7 +832,7 @@ class KernelLibrary:
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), dtype_code(out.dtype), _ptr(block_table),
                 C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks), C.c_int(n),
                 C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
-                C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), _stream()),
+                C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), *mods, _stream()),
                 "paged_attention_general_mma")
             return
         # float32, and sizes the tensor-core forms do not take: float32 arithmetic; a bfloat16 decode step in slices
@@ -845,7 +849,7 @@ class KernelLibrary:
             _ptr(block_table), C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks),
             C.c_int(n), C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
             C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), C.c_int(nsplit), C.c_int(chunk),
-            _ptr(part_o), _ptr(part_ml), _stream()), "paged_attention_general")
+            _ptr(part_o), _ptr(part_ml), *mods, _stream()), "paged_attention_general")
         if nsplit > 1:
             self.launches += 1           # the kernel that adds the slices
 
@@ -861,6 +865,70 @@ class KernelLibrary:
             dtype_code(q_out.dtype), _ptr(k_cache), _ptr(v_cache), dtype_code(k_cache.dtype), _ptr(kv_slot), _ptr(v_keep), _ptr(lam), C.c_int(mix_mode),
             C.c_int(int(write_kv)), C.c_int(T), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
             C.c_int(k_cache.shape[2]), _stream()), "attention_bias_append")
+
+    def attention_unit_norm_append(self, proj, eps, q_out, k_cache, v_cache, kv_slot, nq, nkv, dk, dv, write_kv=True):
+        """From a stacked q | k | v (| more) projection [T, >= nq dk + nkv (dk + dv)]: every q and k head divided by
+        sqrt(mean(x^2) + eps) in float32 (eps None: as projected); q to q_out (float32 or bfloat16), k and v to the pages."""
+        self._check(self.lib.srlm_attention_unit_norm_append(
+            _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), C.c_float(eps if eps else 0.0), _ptr(q_out),
+            dtype_code(q_out.dtype), _ptr(k_cache), _ptr(v_cache), dtype_code(k_cache.dtype), _ptr(kv_slot),
+            C.c_int(int(write_kv)), C.c_int(proj.shape[0]), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
+            C.c_int(k_cache.shape[2]), _stream()), "attention_unit_norm_append")
+
+    def softcap(self, x, cap):
+        """x <- cap * tanh(x / cap), float32 in place."""
+        if x.dtype != torch.float32:
+            raise ShapeError("softcap: float32 values")
+        self._check(self.lib.srlm_softcap(_ptr(x), C.c_float(cap), C.c_longlong(x.numel()), _stream()), "softcap")
+
+    # ---- routed experts ----------------------------------------------------------------------
+    def moe_tile_rows(self) -> int:
+        return int(self.lib.srlm_moe_tile_rows())
+
+    def moe_route(self, logits, bias, top, choice, weight):
+        """logits float32 [T, E] (+ bias float32 [E]) -> choice int32 [T, top], the experts with the largest
+        logits (ties: the lowest index), and weight float32 [T, top], the softmax over the chosen logits."""
+        T, E = logits.shape
+        if logits.dtype != torch.float32 or choice.dtype != torch.int32 or weight.dtype != torch.float32:
+            raise ShapeError("moe_route: float32 logits and weights, int32 choices")
+        self._check(self.lib.srlm_moe_route(_ptr(logits), C.c_longlong(logits.stride(0)), _ptr(bias), C.c_int(T), C.c_int(E),
+                                            C.c_int(top), _ptr(choice), _ptr(weight), _stream()), "moe_route")
+
+    def moe_sort(self, choice, experts, offsets, tiles, pair_of_row, row_of_pair):
+        """The (token, choice) pairs ordered by expert: offsets / tiles int32 [experts + 1] (first row and first
+        tile of each expert), pair_of_row / row_of_pair int32 [pairs]."""
+        self._check(self.lib.srlm_moe_sort(_ptr(choice), C.c_int(choice.numel()), C.c_int(experts), _ptr(offsets),
+                                           _ptr(tiles), _ptr(pair_of_row), _ptr(row_of_pair), _stream()), "moe_sort")
+
+    def moe_grouped(self, a, pair_of_row, pairs_per_token, w, out, offsets, tiles, glu=False, interleaved=False,
+                    limit=0.0, alpha=0.0):
+        """out[row] = a[row's token] . w[row's expert]^T for every row of the sorted pairs (pair_of_row None: row r
+        of ``a`` is row r of ``out``).  w [experts, N, K]; glu: w [experts, 2 N, K] and out gets the clamped GLU of
+        the gate and up halves (interleaved: in blocks of 8 gate rows and 8 up rows, else all gate rows first)."""
+        E, rows, K = w.shape
+        n, N = out.shape
+        if a.shape[1] != K or rows != (2 * N if glu else N):
+            raise ShapeError(f"moe_grouped: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.srlm_moe_grouped_simt(
+            _ptr(a), dtype_code(a.dtype), C.c_longlong(a.stride(0)), _ptr(pair_of_row), C.c_int(pairs_per_token), _ptr(w),
+            dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype), C.c_longlong(out.stride(0)), _ptr(offsets), _ptr(tiles),
+            C.c_int(n), C.c_int(E), C.c_int(N), C.c_int(K), C.c_int(int(glu)), C.c_int(int(interleaved)), C.c_float(limit),
+            C.c_float(alpha), _stream()), "moe_grouped_simt")
+
+    def moe_combine(self, rows, row_of_pair, weight, shared, out):
+        """out[t] = sum over t's choices, in their order, of weight * rows[row of the pair] (+ shared[t])."""
+        T, H = out.shape
+        self._check(self.lib.srlm_moe_combine(
+            _ptr(rows), dtype_code(rows.dtype), C.c_longlong(rows.stride(0)), _ptr(row_of_pair), _ptr(weight), _ptr(shared),
+            _ptr(out), dtype_code(out.dtype), C.c_int(T), C.c_int(weight.shape[1]), C.c_int(H), _stream()), "moe_combine")
+
+    def clamped_glu(self, gate_up, out, limit, alpha):
+        """out [T, F] = g * logistic(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate_up [T, 2 F]:
+        gate columns, then up columns."""
+        T, F = out.shape
+        self._check(self.lib.srlm_clamped_glu(_ptr(gate_up), dtype_code(gate_up.dtype), _ptr(out), dtype_code(out.dtype),
+                                              C.c_int(T), C.c_int(F), C.c_float(limit), C.c_float(alpha), _stream()),
+                    "clamped_glu")
 
     # ---- attention over a cached latent ----------------------------------------------------
     def latent_append(self, proj, c_off, norm_w, eps, rotation, cache, kv_slot, rank, rot):

@@ -25,11 +25,13 @@ class PreNormBlock(Block):
         self.spec = spec
         self.mixer_norm = lookup(NORMS, spec.mixer_norm.kind, "norm")(spec.mixer_norm, p + spec.mixer_norm_name,
                                                                       tensors, mctx)
-        self.ff_norm = lookup(NORMS, spec.feed_forward_norm.kind, "norm")(spec.feed_forward_norm,
-                                                                          p + spec.feed_forward_norm_name, tensors, mctx)
         self.mixer = lookup(MIXERS, spec.mixer.kind, "mixer")(spec.mixer, p, tensors, mctx)
-        self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
-            spec.feed_forward, p, tensors, mctx)
+        self.ff_norm = self.feed_forward = None          # a layer of a mixer alone: x + mixer(norm(x))
+        if spec.feed_forward is not None:
+            self.ff_norm = lookup(NORMS, spec.feed_forward_norm.kind, "norm")(
+                spec.feed_forward_norm, p + spec.feed_forward_norm_name, tensors, mctx)
+            self.feed_forward = lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward")(
+                spec.feed_forward, p, tensors, mctx)
         self.hidden = spec.mixer_norm.size
         self.replayable = all(getattr(part, "replayable", True)
                               for part in (self.mixer_norm, self.ff_norm, self.mixer, self.feed_forward))
@@ -37,17 +39,20 @@ class PreNormBlock(Block):
     @classmethod
     def tensor_decls(cls, spec: LayerSpec, prefix: str = "") -> List[TensorDecl]:
         p = spec.weight_prefix
-        return (lookup(NORMS, spec.mixer_norm.kind, "norm").tensor_decls(spec.mixer_norm, p + spec.mixer_norm_name)
-                + lookup(MIXERS, spec.mixer.kind, "mixer").tensor_decls(spec.mixer, p)
-                + lookup(NORMS, spec.feed_forward_norm.kind, "norm").tensor_decls(spec.feed_forward_norm,
-                                                                                 p + spec.feed_forward_norm_name)
-                + lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward").tensor_decls(
-                    spec.feed_forward, p))
+        decls = (lookup(NORMS, spec.mixer_norm.kind, "norm").tensor_decls(spec.mixer_norm, p + spec.mixer_norm_name)
+                 + lookup(MIXERS, spec.mixer.kind, "mixer").tensor_decls(spec.mixer, p))
+        if spec.feed_forward is not None:
+            decls += (lookup(NORMS, spec.feed_forward_norm.kind, "norm").tensor_decls(spec.feed_forward_norm,
+                                                                                      p + spec.feed_forward_norm_name)
+                      + lookup(FEED_FORWARDS, spec.feed_forward.kind, "feed-forward").tensor_decls(
+                          spec.feed_forward, p))
+        return decls
 
     def fuses(self, ctx) -> bool:
         """Whether this block runs its norms inside the products around them for this step: both parts
         offer forward_fused and the step is small enough for the kernels that carry the fusions."""
-        return (getattr(self.mixer_norm, "fusable", False) and getattr(self.ff_norm, "fusable", False)
+        return (self.feed_forward is not None
+                and getattr(self.mixer_norm, "fusable", False) and getattr(self.ff_norm, "fusable", False)
                 and hasattr(self.mixer, "forward_fused") and hasattr(self.feed_forward, "forward_fused")
                 and self.mixer.can_fuse(ctx) and self.feed_forward.can_fuse(ctx)
                 and not ctx.options.get("unfused_norms", False))
@@ -75,6 +80,8 @@ class PreNormBlock(Block):
         n = ctx.workspace.get("block.normed", T, self.hidden, ctx.dtype)
         self.mixer_norm.apply(residual, pending, n)
         mixed = self.mixer.forward(ctx, n, run_step)
+        if self.feed_forward is None:
+            return mixed                      # the next norm adds it
         self.ff_norm.apply(residual, mixed, n)
         return self.feed_forward.forward(ctx, n)
 

@@ -25,6 +25,8 @@ def tensor_decls(spec: ModelSpec) -> List[TensorDecl]:
     if spec.embed_position is not None:
         decls += lookup(POSITION_ENCODINGS, spec.embed_position.kind, "position encoding").tensor_decls(
             spec.embed_position, spec.embed_position_name)
+    if spec.embed_norm is not None:
+        decls += lookup(NORMS, spec.embed_norm.kind, "norm").tensor_decls(spec.embed_norm, spec.embed_norm_name)
     for layer in spec.layers:
         decls += lookup(BLOCKS, layer.block, "block").tensor_decls(layer)
     decls += lookup(NORMS, spec.final_norm.kind, "norm").tensor_decls(spec.final_norm, spec.final_norm_name)
@@ -75,6 +77,10 @@ class DecoderModel:
             if getattr(cls, "applies", None) != EMBEDDING:
                 raise ConfigError(f"position encoding {spec.embed_position.kind!r} does not add to the embedding")
             self.embed_position = cls(spec.embed_position, mctx, tensors, spec.embed_position_name)
+        self.embed_norm = None
+        if spec.embed_norm is not None:
+            self.embed_norm = lookup(NORMS, spec.embed_norm.kind, "norm")(spec.embed_norm, spec.embed_norm_name,
+                                                                          tensors, mctx)
         self.blocks = [lookup(BLOCKS, layer.block, "block")(layer, tensors, mctx) for layer in spec.layers]
         self.final_norm = lookup(NORMS, spec.final_norm.kind, "norm")(spec.final_norm, spec.final_norm_name,
                                                                       tensors, mctx)
@@ -96,7 +102,13 @@ class DecoderModel:
         H = self.spec.hidden_size
         residual = ctx.workspace.get("residual", ctx.T, H, torch.float32)
         status = ctx.status if ctx.status is not None else self.status
-        ops.embed_gather(ctx.token_ids, self.embed, residual, status[FAULT_TOKEN:FAULT_TOKEN + 1])
+        if self.embed_norm is not None:
+            # the stream starts from the normed rows of the table: gathered beside it, normed into it (float32)
+            rows = ctx.workspace.get("embed.rows", ctx.T, H, torch.float32)
+            ops.embed_gather(ctx.token_ids, self.embed, rows, status[FAULT_TOKEN:FAULT_TOKEN + 1])
+            self.embed_norm.apply(rows, None, residual)
+        else:
+            ops.embed_gather(ctx.token_ids, self.embed, residual, status[FAULT_TOKEN:FAULT_TOKEN + 1])
         if self.embed_position is not None:
             self.embed_position.add_to_embedding(ctx, residual)
         pending = None
@@ -116,6 +128,8 @@ class DecoderModel:
         hn = ctx.workspace.get("final.normed", R, H, ctx.dtype, reserve=64)
         self.final_norm.apply(residual, pending, hn, rows=ctx.logit_rows)
         self.head.into(ctx, hn, logits)
+        if self.spec.logit_softcap is not None:
+            ops.softcap(logits, self.spec.logit_softcap)
         return logits
 
     def weight_bytes(self) -> int:

@@ -1,0 +1,93 @@
+"""A feed-forward of routed experts, plus one expert that every token runs.
+
+    z = W_r h + b                      float32
+    E(h) = the ``top`` experts with the largest z;  w = softmax(z restricted to E(h))
+    out = sum_{e in E(h)} w_e * expert_e(h)  +  shared(h)
+    expert(h) = W_down (g * logistic(alpha g) * (u + 1)),  g = min(W_gate h, limit),  u = clamp(W_up h, -limit, limit)
+
+The pairs (token, chosen expert) are ordered by expert on the device and every expert's rows run through
+one grouped product per projection; a token's result does not depend on what else is in the step, and
+nothing is planned on the host, so decode steps replay from CUDA graphs.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..config.spec import RoutedExpertsSpec
+from ..errors import Unsupported
+from ..kernels import ops
+from ..weights.loader import MATRIX, VECTOR, TensorDecl
+from .base import Part, register_feed_forward
+from .linear import Linear
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts(Part):
+    def __init__(self, spec: RoutedExpertsSpec, prefix: str, tensors: dict, mctx):
+        if spec.activation != "clamped_glu":
+            raise Unsupported(f"routed experts with activation {spec.activation!r} are not implemented")
+        self.spec = spec
+        p, nm = prefix, spec.expert_names
+        self.router = Linear(tensors[p + nm.router], p + nm.router)
+        self.router_bias = tensors[p + nm.router_bias] if spec.router_bias else None
+        each = lambda part: [tensors[p + nm.expert.format(e) + part] for e in range(spec.experts)]
+        # per expert the gate rows, then the up rows: [experts, 2 ff, hidden]; and [experts, hidden, ff]
+        self.gate_up = torch.stack([torch.cat([g, u], dim=0) for g, u in zip(each(nm.gate), each(nm.up))]).contiguous()
+        self.down = torch.stack(each(nm.down)).contiguous()
+        self.shared_gate_up = self.shared_down = None
+        if spec.shared_size:
+            sp = p + nm.shared
+            self.shared_gate_up = Linear(torch.cat([tensors[sp + nm.gate], tensors[sp + nm.up]], dim=0).contiguous(),
+                                         sp + "gate_up")
+            self.shared_down = Linear(tensors[sp + nm.down], sp + nm.down)
+
+    @classmethod
+    def tensor_decls(cls, s: RoutedExpertsSpec, prefix: str) -> List[TensorDecl]:
+        p, nm = prefix, s.expert_names
+        H = s.hidden_size
+        decls = []
+        for e in range(s.experts):
+            ep = p + nm.expert.format(e)
+            decls += [TensorDecl(ep + nm.gate, (s.intermediate_size, H), MATRIX),
+                      TensorDecl(ep + nm.up, (s.intermediate_size, H), MATRIX),
+                      TensorDecl(ep + nm.down, (H, s.intermediate_size), MATRIX)]
+        decls.append(TensorDecl(p + nm.router, (s.experts, H), MATRIX))
+        if s.router_bias:
+            decls.append(TensorDecl(p + nm.router_bias, (s.experts,), VECTOR))
+        if s.shared_size:
+            sp = p + nm.shared
+            decls += [TensorDecl(sp + nm.gate, (s.shared_size, H), MATRIX), TensorDecl(sp + nm.up, (s.shared_size, H), MATRIX),
+                      TensorDecl(sp + nm.down, (H, s.shared_size), MATRIX)]
+        return decls
+
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        s = self.spec
+        T, H = x.shape
+        ws = ctx.workspace
+        pairs = T * s.top
+        # the router in float32: its input may be the activation dtype's rounding of the normed stream
+        logits = self.router(ctx, x, "moe.logits", out_dtype=torch.float32)
+        choice = ws.get("moe.choice", T, s.top, torch.int32)
+        weight = ws.get("moe.weight", T, s.top, torch.float32)
+        ops.moe_route(logits, self.router_bias, s.top, choice, weight)
+        heads = ws.get("moe.heads", 2, s.experts + 1, torch.int32, reserve=2)
+        order = ws.get("moe.order", 2 * T, s.top, torch.int32, reserve=2 * ws.max_tokens)
+        offsets, tiles = heads[0], heads[1]
+        pair_of_row, row_of_pair = order[:T].view(-1), order[T:].view(-1)
+        ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair)
+        y = ws.get("moe.y", pairs, s.intermediate_size, ctx.dtype, reserve=ws.max_tokens * s.top)
+        ops.moe_grouped(x, pair_of_row, s.top, self.gate_up, y, offsets, tiles, glu=True, limit=s.limit,
+                        alpha=s.glu_alpha)
+        rows = ws.get("moe.rows", pairs, H, torch.float32, reserve=ws.max_tokens * s.top)
+        ops.moe_grouped(y, None, 1, self.down, rows, offsets, tiles)
+        shared = None
+        if self.shared_gate_up is not None:
+            gu = self.shared_gate_up(ctx, x, "moe.shared_gu", out_dtype=torch.float32)
+            ys = ws.get("moe.shared_y", T, s.shared_size, ctx.dtype)
+            ops.clamped_glu(gu, ys, s.shared_limit, s.glu_alpha)
+            shared = self.shared_down(ctx, ys, "moe.shared_out")
+        out = ws.get("moe.out", T, H, ctx.dtype)
+        ops.moe_combine(rows, row_of_pair, weight, shared, out)
+        return out
