@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
                     [--shape 8b|14b|32b] [--workload decode|mixed]
-    python bench.py --design nekedra [--design-size 2048|4096]
+    python bench.py --design nekedra|tonanex [--design-size 2048|4096]
 
 A "step" is one decode step: every request of the batch gets its next token.
 The default run has the sizes of the 8B configuration (36 layers, hidden 4096,
@@ -555,6 +555,23 @@ def nekedra_config(size: dict, kinds) -> dict:
             "layers": [{"type": k, "mixer": mixers[k], "mlp": {"kind": "dense", "ff": 3 * W}} for k in kinds]}
 
 
+TONANEX_WINDOW = 1024
+TONANEX_EXPERTS, TONANEX_TOP = 16, 4
+
+
+def tonanex_config(size: dict, kinds) -> dict:
+    """A Tonanex configuration whose layers have the sizes of a Qwen3 layer of the same width: heads of 128 for keys
+    and values, a window of 1,024 tokens; a dense feed-forward of three widths, or 16 experts of half a width of which
+    a token runs 4, plus a shared one of one width: three widths of feed-forward rows a token, as in the dense layer."""
+    W, H, G = size["width"], size["heads"], size["kv_heads"]
+    mixer = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": TONANEX_WINDOW}}
+    mlps = {"dense": {"kind": "dense", "ff": 3 * W},
+            "moe": {"kind": "moe", "expert": {"ff": W // 2, "limit": 7.0},
+                    "router": {"experts": TONANEX_EXPERTS, "top": TONANEX_TOP}, "shared": {"ff": W, "limit": 7.0}}}
+    return {"architecture": "Tonanex", "width": W, "vocab": DESIGN_VOCAB, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": mlps[k]} for k in kinds]}
+
+
 def qwen3_config(size: dict) -> dict:
     return dict(BASE, num_hidden_layers=DESIGN_LAYERS, hidden_size=size["width"], num_attention_heads=size["heads"],
                 num_key_value_heads=size["kv_heads"], intermediate_size=3 * size["width"], vocab_size=DESIGN_VOCAB)
@@ -570,13 +587,17 @@ def run_design(args) -> dict:
     stacks = {"qwen3": None, "nekedra attention": ["attention"] * DESIGN_LAYERS,
               "nekedra latent": ["latent_attention"] * DESIGN_LAYERS, "nekedra delta": ["delta"] * DESIGN_LAYERS,
               "nekedra mixed": ["latent_attention", "delta", "attention", "delta"]}
-    out = {"metric": "nekedra_beside_qwen3", "layers": DESIGN_LAYERS, "prefill_tokens": PREFILL_TOKENS,
+    make = nekedra_config
+    if args.design == "tonanex":
+        stacks = {"qwen3": None, "tonanex dense": ["dense"] * DESIGN_LAYERS, "tonanex experts": ["moe"] * DESIGN_LAYERS}
+        make = tonanex_config
+    out = {"metric": args.design + "_beside_qwen3", "layers": DESIGN_LAYERS, "prefill_tokens": PREFILL_TOKENS,
            "decode_batch": batch, "decode_context": context, "dtype": "bf16", "data": "synthetic", "sizes": {}}
     sizes = [args.design_size] if args.design_size else sorted(DESIGN_SIZES)
     for name in sizes:
         size, rows = DESIGN_SIZES[name], {}
         for label, kinds in stacks.items():
-            cfg = qwen3_config(size) if kinds is None else nekedra_config(size, kinds)
+            cfg = qwen3_config(size) if kinds is None else make(size, kinds)
             eng = build_engine(cfg, DESIGN_LAYERS, batch + 1, batch * (context + MAX_GROWTH) + PREFILL_TOKENS,
                                PREFILL_TOKENS)
             randomize_cache(eng)
@@ -615,9 +636,9 @@ def main() -> int:
     ap.add_argument("--only-prefill", action="store_true", help="run just the 2,048-token prefill (for profilers)")
     ap.add_argument("--streaming-kernel", action="store_true",
                     help="steps of up to 8 tokens on the weight-streaming mma.sync kernel instead of the tensor-core one")
-    ap.add_argument("--design", default=None, choices=["nekedra"],
-                    help="instead of the default workload: prefill and decode of Nekedra stacks beside the Qwen3 "
-                         "decoder at equal layer sizes")
+    ap.add_argument("--design", default=None, choices=["nekedra", "tonanex"],
+                    help="instead of the default workload: prefill and decode of Nekedra or Tonanex stacks beside the "
+                         "Qwen3 decoder at equal layer sizes")
     ap.add_argument("--design-size", default=None, choices=sorted(DESIGN_SIZES), help="one width of --design")
     ap.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
                     help="repeat the block of --steps steps until this much is timed (0: one block, for profilers)")

@@ -84,8 +84,10 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
   int first_key = window > 0 ? max(0, min_pos - window + 1) : 0;
   int last_key = max_pos;
   if (sliced) {                                            // kv_chunk is a multiple of kKeys
-    first_key = max(first_key, (int)blockIdx.x * kv_chunk);
-    last_key = min(last_key, ((int)blockIdx.x + 1) * kv_chunk - 1);
+    // the slices lie over the keys the rows can see: from the key block that holds the window's first key
+    const int base = (first_key / kKeys) * kKeys;
+    first_key = max(first_key, base + (int)blockIdx.x * kv_chunk);
+    last_key = min(last_key, base + ((int)blockIdx.x + 1) * kv_chunk - 1);
   }
 
   for (int jb = (first_key / kKeys) * kKeys; jb <= last_key; jb += kKeys) {

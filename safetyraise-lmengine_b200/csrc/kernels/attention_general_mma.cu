@@ -344,8 +344,10 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
   int first_key = window > 0 ? max(0, start + r0 / G - window + 1) : 0;
   int last_key = max_pos;
   if (nsplit > 1) {
-    first_key = max(first_key, slice * kv_chunk);
-    last_key = min(last_key, (slice + 1) * kv_chunk - 1);
+    // the slices lie over the keys the rows can see: from the key tile that holds the window's first key
+    const int base = (first_key / kDecKeys) * kDecKeys;
+    first_key = max(first_key, base + slice * kv_chunk);
+    last_key = min(last_key, base + (slice + 1) * kv_chunk - 1);
   }
   const int jb0 = (first_key / kDecKeys) * kDecKeys;
   const int kvec = dk / 8, vvec = dv / 8;

@@ -211,6 +211,128 @@ moe_grouped_simt_kernel(const TA* __restrict__ A, long long lda, const int* __re
   }
 }
 
+// ---- the grouped products on bfloat16 tensor cores (mma.sync m16n8k16, float32 sums) -------------------------------
+// A block of eight warps takes one tile of kTile rows of one expert and MBN weight rows, and walks K in slabs
+// of MBK through a ring of cp.async stages (rows of A gathered by the pair's token).  Warps lie 2 x 4 over the
+// tile: 32 rows x 32 weight rows each.  GLU: the weight rows come in blocks of 16 (8 gate rows, then the 8 up
+// rows of the same features), so a thread that holds a gate sum in one 8-column tile holds the up sum of the
+// same feature and row in the next tile, and the activation needs no exchange: C gets MBN / 2 features a block.
+constexpr int MBN = 128, MBK = 32, MPAD = 8, MSTAGES = 3;
+
+__device__ __forceinline__ void moe_ldmatrix_x4(uint32_t (&r)[4], const bf16* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void moe_mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void moe_cp_async_16(void* dst, const void* src, bool full) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int n = full ? 16 : 0;                               // 0: sixteen zero bytes, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n));
+}
+
+template <typename TO, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_grouped_mma_kernel(const bf16* __restrict__ A, long long lda, const int* __restrict__ pair_of_row, int pairs_per_token,
+                       const bf16* __restrict__ W, TO* __restrict__ C, long long ldc, const int* __restrict__ offsets,
+                       const int* __restrict__ tiles, int E, int NW, int K, float limit, float alpha) {
+  pdl_wait();
+  pdl_trigger();
+  // NW: weight rows per expert (twice the features when GLU)
+  __shared__ __align__(16) bf16 As[MSTAGES][kTile][MBK + MPAD];
+  __shared__ __align__(16) bf16 Ws[MSTAGES][MBN][MBK + MPAD];
+  __shared__ int a_row[kTile];
+  int expert, row0, row_end;
+  if (!tile_home(offsets, tiles, E, blockIdx.y, expert, row0, row_end)) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp >> 2, wn = warp & 3;                  // the warp's 32 rows and 32 weight rows of the tile
+  const int n0 = blockIdx.x * MBN;
+  if (tid < kTile) {
+    const int row = row0 + tid;
+    a_row[tid] = row < row_end ? (pair_of_row ? pair_of_row[row] / pairs_per_token : row) : -1;
+  }
+  __syncthreads();
+  const bf16* We = W + (size_t)expert * NW * K;
+  // a thread's copies of a stage: one 16-byte piece of A (64 rows x 4 pieces), two of W (128 rows x 4 pieces)
+  const int ar = tid >> 2, ac = (tid & 3) * 8;
+  const int a_src = a_row[ar];
+  auto fetch = [&](int k0, int st) {
+    moe_cp_async_16(&As[st][ar][ac], A + (size_t)(a_src < 0 ? 0 : a_src) * lda + k0 + ac, a_src >= 0 && k0 + ac < K);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int wr = ar + i * 64, n = n0 + wr;
+      moe_cp_async_16(&Ws[st][wr][ac], We + (size_t)(n < NW ? n : 0) * K + k0 + ac, n < NW && k0 + ac < K);
+    }
+    asm volatile("cp.async.commit_group;" ::);
+  };
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+  const int slabs = (K + MBK - 1) / MBK;
+  for (int s = 0; s < MSTAGES - 1; ++s) {
+    if (s < slabs) fetch(s * MBK, s);
+    else asm volatile("cp.async.commit_group;" ::);
+  }
+  for (int s = 0; s < slabs; ++s) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(MSTAGES - 2));
+    __syncthreads();                                        // slab s has landed; the stage of slab s - 1 is free
+    if (s + MSTAGES - 1 < slabs) fetch((s + MSTAGES - 1) * MBK, (s + MSTAGES - 1) % MSTAGES);
+    else asm volatile("cp.async.commit_group;" ::);
+    const int st = s % MSTAGES;
+#pragma unroll
+    for (int kk = 0; kk < MBK; kk += 16) {
+      uint32_t a[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        moe_ldmatrix_x4(a[i], &As[st][wm * 32 + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int j2 = 0; j2 < 2; ++j2) {
+        uint32_t b[4];
+        moe_ldmatrix_x4(b, &Ws[st][wn * 32 + j2 * 16 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          moe_mma_bf16(acc[i][2 * j2], a[i], b[0], b[1]);
+          moe_mma_bf16(acc[i][2 * j2 + 1], a[i], b[2], b[3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = row0 + wm * 32 + i * 16 + (lane >> 2) + 8 * half;
+      if (row >= row_end) continue;
+      if (GLU) {
+#pragma unroll
+        for (int j2 = 0; j2 < 2; ++j2)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int f = (n0 + wn * 32 + j2 * 16) / 2 + (lane & 3) * 2 + c;
+            if (2 * f < NW)
+              C[(size_t)row * ldc + f] = from_float<TO>(clamped_glu(acc[i][2 * j2][2 * half + c], acc[i][2 * j2 + 1][2 * half + c],
+                                                                    limit, alpha));
+          }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int n = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
+            if (n < NW) C[(size_t)row * ldc + n] = from_float<TO>(acc[i][j][2 * half + c]);
+          }
+      }
+    }
+}
+
 // out[t, :] = sum_c weight[t, c] * rows[row_of_pair[t * top + c], :]  (+ shared[t, :]), float32 sums in the order of c
 template <typename TR, typename TA>
 __global__ void moe_combine_kernel(const TR* __restrict__ rows, long long ldr, const int* __restrict__ row_of_pair,
@@ -340,5 +462,32 @@ extern "C" int srlm_clamped_glu(const void* in, int in_dtype, void* out, int out
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_GLU(bf16, bf16);
   else return refuse(ST_BAD_DTYPE, "clamped_glu: input dtype %d with output dtype %d", in_dtype, out_dtype);
 #undef SRLM_GLU
+  return launched();
+}
+
+// The same products on bfloat16 tensor cores: K a multiple of 8, 16-byte aligned operands; with glu the weight
+// rows interleaved in blocks of 16 (8 gate rows, 8 up rows) and N (features) a multiple of 8.
+extern "C" int srlm_moe_grouped_mma_takes(int N, int K, int glu) { return K > 0 && K % 8 == 0 && N > 0 && (!glu || N % 8 == 0); }
+
+extern "C" int srlm_moe_grouped_mma(const void* A, long long lda, const int* pair_of_row, int pairs_per_token, const void* W,
+                                    void* C, int c_dtype, long long ldc, const int* offsets, const int* tiles, int n, int E,
+                                    int N, int K, int glu, float limit, float alpha, cudaStream_t stream) {
+  if (n <= 0) return ST_OK;
+  if (E <= 0 || !srlm_moe_grouped_mma_takes(N, K, glu) || lda < K || lda % 8 || ldc < N || (pair_of_row && pairs_per_token <= 0))
+    return refuse(ST_BAD_SIZE, "moe_grouped_mma: experts=%d N=%d K=%d lda=%lld ldc=%lld", E, N, K, lda, ldc);
+  if ((((uintptr_t)A | (uintptr_t)W) & 15) != 0) return refuse(ST_BAD_ALIGN, "moe_grouped_mma: operands must be 16-byte aligned");
+  const int bound = tile_bound(n, E);
+  if (bound > 65535) return refuse(ST_BAD_SIZE, "moe_grouped_mma: %d pairs over %d experts exceed 65535 tiles", n, E);
+  const int NW = glu ? 2 * N : N;
+  dim3 grid((NW + MBN - 1) / MBN, bound);
+#define SRLM_GROUPED_MMA(TO, G)                                                                                          \
+  launch_pdl(moe_grouped_mma_kernel<TO, G>, grid, dim3(256), 0, stream, (const bf16*)A, lda, pair_of_row, pairs_per_token, \
+             (const bf16*)W, (TO*)C, ldc, offsets, tiles, E, NW, K, limit, alpha)
+  if (c_dtype == DT_BF16 && glu) SRLM_GROUPED_MMA(bf16, true);
+  else if (c_dtype == DT_F32 && glu) SRLM_GROUPED_MMA(float, true);
+  else if (c_dtype == DT_BF16) SRLM_GROUPED_MMA(bf16, false);
+  else if (c_dtype == DT_F32) SRLM_GROUPED_MMA(float, false);
+  else return refuse(ST_BAD_DTYPE, "moe_grouped_mma: output dtype %d", c_dtype);
+#undef SRLM_GROUPED_MMA
   return launched();
 }

@@ -74,6 +74,7 @@ class KernelLibrary:
         self.general_attention_on_tensor_cores = True   # its prompts and portions: mma.sync, when the sizes fit
         self.latent_prompts_in_head_space = True        # latent attention: prompts form per-head keys and values
         self.sinks_in_tcgen05_prefill = True            # attention with sinks, heads of 128: prompts on the tcgen05 kernel
+        self.grouped_products_on_tensor_cores = True    # routed experts in bfloat16: mma.sync, when the sizes fit
 
     @property
     def lib(self):
@@ -803,8 +804,10 @@ class KernelLibrary:
         if (tensor_cores and ctx.max_q_len <= 4
                 and self.lib.srlm_attention_general_decode_takes(C.c_int(dk), C.c_int(dv), from_keys)):
             rows_padded = (ctx.max_q_len * g + 15) // 16 * 16
-            nsplit, chunk = self.attention_split(n, nkv * (rows_padded // 16), ctx.kv_bound, max_slices=64)
-            if not self.split_general_attention or window:      # a window's keys: one block walks them
+            # with a window the slices lie over the keys a row tile can see, not over the whole context
+            span = min(ctx.kv_bound, window + ctx.max_q_len + 64) if window else ctx.kv_bound
+            nsplit, chunk = self.attention_split(n, nkv * (rows_padded // 16), span, max_slices=64)
+            if not self.split_general_attention:
                 nsplit, chunk = 1, 0
             part_o = part_ml = None
             if nsplit > 1:
@@ -837,8 +840,9 @@ class KernelLibrary:
             return
         # float32, and sizes the tensor-core forms do not take: float32 arithmetic; a bfloat16 decode step in slices
         nsplit, chunk, part_o, part_ml = 1, 0, None, None
-        if bf16 and decode and not window and self.split_general_attention:
-            nsplit, chunk = self.attention_split(n, nkv, ctx.kv_bound, max_slices=64)
+        if bf16 and decode and self.split_general_attention:
+            span = min(ctx.kv_bound, window + ctx.max_q_len + 64) if window else ctx.kv_bound
+            nsplit, chunk = self.attention_split(n, nkv, span, max_slices=64)
             if nsplit > 1:
                 part_o = ctx.workspace.get("attn.general_part_o", n * nkv * nsplit * self.GENERAL_ROWS, dv,
                                            torch.float32, reserve=0)
@@ -909,6 +913,15 @@ class KernelLibrary:
         n, N = out.shape
         if a.shape[1] != K or rows != (2 * N if glu else N):
             raise ShapeError(f"moe_grouped: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+        if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and (interleaved or not glu) and a.stride(0) % 8 == 0
+                and self.grouped_products_on_tensor_cores
+                and self.lib.srlm_moe_grouped_mma_takes(C.c_int(N), C.c_int(K), C.c_int(int(glu)))):
+            self._check(self.lib.srlm_moe_grouped_mma(
+                _ptr(a), C.c_longlong(a.stride(0)), _ptr(pair_of_row), C.c_int(pairs_per_token), _ptr(w), _ptr(out),
+                dtype_code(out.dtype), C.c_longlong(out.stride(0)), _ptr(offsets), _ptr(tiles), C.c_int(n), C.c_int(E),
+                C.c_int(N), C.c_int(K), C.c_int(int(glu)), C.c_float(limit), C.c_float(alpha), _stream()),
+                "moe_grouped_mma")
+            return
         self._check(self.lib.srlm_moe_grouped_simt(
             _ptr(a), dtype_code(a.dtype), C.c_longlong(a.stride(0)), _ptr(pair_of_row), C.c_int(pairs_per_token), _ptr(w),
             dtype_code(w.dtype), _ptr(out), dtype_code(out.dtype), C.c_longlong(out.stride(0)), _ptr(offsets), _ptr(tiles),

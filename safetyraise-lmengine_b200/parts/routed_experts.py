@@ -33,8 +33,17 @@ class RoutedExperts(Part):
         self.router = Linear(tensors[p + nm.router], p + nm.router)
         self.router_bias = tensors[p + nm.router_bias] if spec.router_bias else None
         each = lambda part: [tensors[p + nm.expert.format(e) + part] for e in range(spec.experts)]
-        # per expert the gate rows, then the up rows: [experts, 2 ff, hidden]; and [experts, hidden, ff]
-        self.gate_up = torch.stack([torch.cat([g, u], dim=0) for g, u in zip(each(nm.gate), each(nm.up))]).contiguous()
+        # [experts, 2 ff, hidden] and [experts, hidden, ff].  For the tensor-core product the gate and up rows are
+        # interleaved in blocks of 16 (8 gate rows, then the 8 up rows of the same features), so that its epilogue
+        # holds both halves of a feature; otherwise per expert the gate rows, then the up rows.
+        I, H = spec.intermediate_size, spec.hidden_size
+        self.interleaved = (mctx.dtype == torch.bfloat16 and I % 8 == 0 and H % 8 == 0
+                            and tensors[p + nm.expert.format(0) + nm.gate].dtype == torch.bfloat16)
+        if self.interleaved:
+            pair = lambda g, u: torch.stack([g.view(I // 8, 8, H), u.view(I // 8, 8, H)], dim=1).reshape(2 * I, H)
+        else:
+            pair = lambda g, u: torch.cat([g, u], dim=0)
+        self.gate_up = torch.stack([pair(g, u) for g, u in zip(each(nm.gate), each(nm.up))]).contiguous()
         self.down = torch.stack(each(nm.down)).contiguous()
         self.shared_gate_up = self.shared_down = None
         if spec.shared_size:
@@ -78,8 +87,8 @@ class RoutedExperts(Part):
         pair_of_row, row_of_pair = order[:T].view(-1), order[T:].view(-1)
         ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair)
         y = ws.get("moe.y", pairs, s.intermediate_size, ctx.dtype, reserve=ws.max_tokens * s.top)
-        ops.moe_grouped(x, pair_of_row, s.top, self.gate_up, y, offsets, tiles, glu=True, limit=s.limit,
-                        alpha=s.glu_alpha)
+        ops.moe_grouped(x, pair_of_row, s.top, self.gate_up, y, offsets, tiles, glu=True, interleaved=self.interleaved,
+                        limit=s.limit, alpha=s.glu_alpha)
         rows = ws.get("moe.rows", pairs, H, torch.float32, reserve=ws.max_tokens * s.top)
         ops.moe_grouped(y, None, 1, self.down, rows, offsets, tiles)
         shared = None
