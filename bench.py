@@ -175,6 +175,16 @@ def fill_contexts(eng, batch: int, context: int):
     return slots
 
 
+def rewind(eng, slots, length: int) -> None:
+    """The contexts back to `length` tokens each, where the cache can: a group with a window has given back the pages
+    behind it, and its contexts stay as long as they have grown (the pool has room for that growth)."""
+    for s in slots:
+        try:
+            eng.cache.truncate(s, length)
+        except ValueError:
+            pass
+
+
 def blocks_for(steps: int, warmup: int, ms_per_step: float, min_seconds: float) -> int:
     """How many blocks of `steps` steps: enough for `min_seconds`, within the growth a context is allowed."""
     want = math.ceil(min_seconds * 1000.0 / max(ms_per_step * steps, 1e-3))
@@ -206,8 +216,7 @@ def time_decode(eng, slots, context: int, steps: int, warmup: int, min_seconds: 
         b.record()
         torch.cuda.synchronize()
         half.append(a.elapsed_time(b))
-    for s in slots:
-        eng.cache.truncate(s, context + warmup)
+    rewind(eng, slots, context + warmup)
     nblocks = blocks_for(steps, warmup, statistics.median(half), min_seconds)
     block_ms, launches = [], 0
     for _ in range(nblocks):
@@ -223,8 +232,7 @@ def time_decode(eng, slots, context: int, steps: int, warmup: int, min_seconds: 
         block_ms.append(a.elapsed_time(b))
         launches = ops.launches - before
     grown = warmup + nblocks * steps
-    for s in slots:
-        eng.cache.truncate(s, context)
+    rewind(eng, slots, context)
     return {"ms_per_step": statistics.median(block_ms) / steps, "device_half_ms": statistics.median(half),
             "blocks": nblocks, "mean_context": context + warmup + (grown - warmup) // 2, "launches": launches,
             "timed_seconds": sum(block_ms) / 1000.0}
@@ -343,8 +351,7 @@ def kernel_table(eng, slots, context: int, top: int = 8):
         table = ops.end_timing()
     finally:
         eng.use_graphs = graphs
-        for s in slots:
-            eng.cache.truncate(s, context)
+        rewind(eng, slots, context)
     total = sum(ms for _, ms in table.values()) or 1.0
     rows = sorted(table.items(), key=lambda kv: -kv[1][1])[:top]
     return {name: {"launches": n, "ms": round(ms, 3), "share": round(ms / total, 3)} for name, (n, ms) in rows}

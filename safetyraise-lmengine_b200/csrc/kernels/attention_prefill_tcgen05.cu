@@ -68,6 +68,9 @@ struct Args {
   // optional, one per query head: a term exp(sink) in the softmax denominator that has no key and no value.
   // It is the state a row's running softmax starts from (maximum = sink, sum = 1); with key slices, slice 0's.
   const float* sinks;
+  // optional, per query head: a factor on the scaled scores, and a penalty weight * ln(1 + rate * distance to the key)
+  // taken off them (ScoreMods in common.cuh); applied to a row of S in registers before its maximum is formed
+  ScoreMods mods;
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -212,6 +215,27 @@ __device__ __forceinline__ void load_row(uint32_t s_addr, Row& r) {
   tmem_ld32(s_addr + 64, r.c);
   tmem_ld32(s_addr + 96, r.d);
   tmem_wait_ld();
+}
+// S <- S * factor - weight_q * log2(1 + rate * distance), distance = dist0 - column (not below 0: columns behind the
+// row's position are masked later).  weight_q is the head's weight over the score scale in log2 units, so that the
+// row, once multiplied by that scale like a plain row, holds score * log2(e).
+__device__ __forceinline__ float lg2(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void modify_row(Row& r, float factor, float weight_q, float rate, float dist0) {
+  auto part = [&](uint32_t (&v)[32], int c) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float d = fmaxf(dist0 - (float)(c + j), 0.f);
+      v[j] = __float_as_uint(fmaf(-weight_q, lg2(fmaf(rate, d, 1.f)), __uint_as_float(v[j]) * factor));
+    }
+  };
+  part(r.a, 0);
+  part(r.b, 32);
+  part(r.c, 64);
+  part(r.d, 96);
 }
 // The maximum of the keys [k_lo, k_hi) of the row (all 128 keys when not MASKED).
 template <bool MASKED>
@@ -517,6 +541,16 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
       m_run = a.sinks[kvh * g + rs % g] * 1.4426950408889634f;      // in log2 units, like the scaled scores
       l_run = 1.f;
     }
+    const bool modified = a.mods.head_scale || a.mods.pen_weight;
+    float factor = 1.f, weight_q = 0.f, rate = 0.f;
+    if (modified) {
+      const int h = kvh * g + min(r, r_end - 1) % g;
+      if (a.mods.head_scale) factor = a.mods.head_scale[h];
+      if (a.mods.pen_weight) {
+        weight_q = a.mods.pen_weight[h] / a.scale_log2;
+        rate = a.mods.pen_rate[h];
+      }
+    }
     bool ok = true;
     for (int t = 0; t < n_tiles && ok; ++t) {
       const int jb = jb0 + t * KT;
@@ -527,6 +561,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, cons
       const int k_lo = max(0, lo - jb), k_hi = min(KT, pos - jb + 1);
       Row srow;
       load_row(s_addr, srow);
+      if (modified) modify_row(srow, factor, weight_q, rate, (float)(pos - jb));
       const float mx = (full ? row_max<false>(srow, 0, KT) : row_max<true>(srow, k_lo, k_hi)) * a.scale_log2;
       // the reference of the exponentials moves only when the maximum has grown by more than 2^8
       const bool grow = mx > m_run + RESCALE_ABOVE || m_run == -CUDART_INF_F;
@@ -724,8 +759,11 @@ static int prefill_tcgen05_entry(const void* q, const void* k_cache, const void*
                                  const int* cu_q, const int* kv_lens, const int* work, int n_work,
                                  int nq, int nkv, int hd, int page_size, float scale, int window,
                                  int tiles_per_block, int nsplit, int kv_chunk, float* part_o,
-                                 float* part_ml, const float* sinks, int* err_flag, cudaStream_t stream) {
+                                 float* part_ml, const float* sinks, int* err_flag, cudaStream_t stream,
+                                 ScoreMods mods = ScoreMods{nullptr, nullptr, nullptr}) {
   if (n_work <= 0) return ST_OK;
+  if ((mods.pen_weight == nullptr) != (mods.pen_rate == nullptr))
+    return refuse(ST_BAD_SIZE, "attention_prefill_tcgen05: a distance penalty needs its weight and its rate");
   if (nsplit < 1) nsplit = 1;
   if (nsplit > 1 && (nsplit > 32 || kv_chunk <= 0 || kv_chunk % fmha::KT || !part_o || !part_ml))
     return refuse(ST_BAD_SIZE, "attention_prefill_tcgen05: nsplit=%d kv_chunk=%d (slices of whole key tiles, at most 32, "
@@ -749,7 +787,7 @@ static int prefill_tcgen05_entry(const void* q, const void* k_cache, const void*
     configured = true;
   }
   fmha::Args a{(const bf16*)q, (bf16*)out, block_table, table_stride, cu_q, kv_lens, work, nq, nkv, page_size,
-               tiles_per_block, scale * 1.4426950408889634f, window, err_flag, nsplit, kv_chunk, part_o, part_ml, sinks};
+               tiles_per_block, scale * 1.4426950408889634f, window, err_flag, nsplit, kv_chunk, part_o, part_ml, sinks, mods};
   launch_pdl(fmha::attention_prefill_tcgen05_kernel, dim3(n_work * nkv, nsplit), dim3(fmha::THREADS), SMEM, stream,
              *mk, *mv, a);
   if (nsplit > 1)
@@ -780,4 +818,20 @@ extern "C" int srlm_paged_attention_prefill_tcgen05_sinks(const void* q, const v
   return prefill_tcgen05_entry(q, k_cache, v_cache, out, num_pages, block_table, table_stride, cu_q, kv_lens, work, n_work,
                                nq, nkv, hd, page_size, scale, window, tiles_per_block, nsplit, kv_chunk, part_o, part_ml,
                                sinks, err_flag, stream);
+}
+
+// The same with per-head changes to the scores (each float32 [nq] or null): a factor on the scaled scores, and a
+// penalty pen_weight * ln(1 + pen_rate * (query position - key position)) taken off them; sinks as above, or null.
+extern "C" int srlm_paged_attention_prefill_tcgen05_mods(const void* q, const void* k_cache, const void* v_cache,
+                                                         void* out, long long num_pages, const int* block_table,
+                                                         int table_stride, const int* cu_q, const int* kv_lens,
+                                                         const int* work, int n_work, int nq, int nkv, int hd,
+                                                         int page_size, float scale, int window, int tiles_per_block,
+                                                         int nsplit, int kv_chunk, float* part_o, float* part_ml,
+                                                         const float* sinks, const float* head_scale,
+                                                         const float* pen_weight, const float* pen_rate, int* err_flag,
+                                                         cudaStream_t stream) {
+  return prefill_tcgen05_entry(q, k_cache, v_cache, out, num_pages, block_table, table_stride, cu_q, kv_lens, work, n_work,
+                               nq, nkv, hd, page_size, scale, window, tiles_per_block, nsplit, kv_chunk, part_o, part_ml,
+                               sinks, err_flag, stream, ScoreMods{head_scale, pen_weight, pen_rate});
 }

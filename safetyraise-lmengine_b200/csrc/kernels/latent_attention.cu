@@ -200,15 +200,15 @@ __global__ void latent_rotate_q_kernel(const TP* __restrict__ proj, long long ld
 }
 
 // out[t, h, :] = in[t, h, :] * sigmoid(proj[t, g_off + h])   (g_off < 0: no gate, a change of type only)
-template <typename TP, typename TA>
-__global__ void head_gate_kernel(const float* __restrict__ in, const TP* __restrict__ proj, long long ldp, int g_off,
-                                 TA* __restrict__ out, int heads, int dv) {
+template <typename TI, typename TP, typename TA>
+__global__ void head_gate_kernel(const TI* in, const TP* __restrict__ proj, long long ldp, int g_off,
+                                 TA* out, int heads, int dv) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   const int t = blockIdx.x;
   for (int idx = threadIdx.x; idx < heads * dv; idx += blockDim.x) {
     const float g = g_off >= 0 ? 1.f / (1.f + expf(-to_float(proj[(size_t)t * ldp + g_off + idx / dv]))) : 1.f;
-    out[(size_t)t * heads * dv + idx] = from_float<TA>(in[(size_t)t * heads * dv + idx] * g);
+    out[(size_t)t * heads * dv + idx] = from_float<TA>(to_float(in[(size_t)t * heads * dv + idx]) * g);
   }
 }
 
@@ -298,16 +298,19 @@ extern "C" int srlm_latent_rotate_q(const void* proj, int proj_dtype, long long 
   return launched();
 }
 
-extern "C" int srlm_head_gate(const float* in, const void* proj, int proj_dtype, long long ldp, int g_off, void* out,
-                              int out_dtype, int T, int heads, int dv, cudaStream_t stream) {
+// in: float32, or bfloat16 (then out may be the same buffer: an element is read and written by one thread)
+extern "C" int srlm_head_gate(const void* in, int in_dtype, const void* proj, int proj_dtype, long long ldp, int g_off,
+                              void* out, int out_dtype, int T, int heads, int dv, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
   if (heads <= 0 || dv <= 0 || (g_off >= 0 && ldp < g_off + heads))
     return refuse(ST_BAD_SIZE, "head_gate: heads=%d dv=%d g_off=%d ldp=%lld", heads, dv, g_off, ldp);
-#define SRLM_GATE(TP, TA) launch_pdl(head_gate_kernel<TP, TA>, dim3(T), dim3(256), 0, stream, in, (const TP*)proj, ldp, g_off, (TA*)out, heads, dv)
-  if (proj_dtype == DT_F32 && out_dtype == DT_F32) SRLM_GATE(float, float);
-  else if (proj_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_GATE(float, bf16);
-  else if (proj_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_GATE(bf16, bf16);
-  else return refuse(ST_BAD_DTYPE, "head_gate: projection dtype %d with output dtype %d", proj_dtype, out_dtype);
+#define SRLM_GATE(TI, TP, TA) launch_pdl(head_gate_kernel<TI, TP, TA>, dim3(T), dim3(256), 0, stream, (const TI*)in, (const TP*)proj, ldp, g_off, (TA*)out, heads, dv)
+  if (in_dtype == DT_F32 && proj_dtype == DT_F32 && out_dtype == DT_F32) SRLM_GATE(float, float, float);
+  else if (in_dtype == DT_F32 && proj_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_GATE(float, float, bf16);
+  else if (in_dtype == DT_F32 && proj_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_GATE(float, bf16, bf16);
+  else if (in_dtype == DT_BF16 && proj_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_GATE(bf16, float, bf16);
+  else if (in_dtype == DT_BF16 && proj_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_GATE(bf16, bf16, bf16);
+  else return refuse(ST_BAD_DTYPE, "head_gate: input dtype %d, projection dtype %d, output dtype %d", in_dtype, proj_dtype, out_dtype);
 #undef SRLM_GATE
   return launched();
 }

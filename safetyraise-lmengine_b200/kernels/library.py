@@ -471,14 +471,21 @@ class KernelLibrary:
 
     def paged_attention_prefill_tcgen05(self, q, k_cache, v_cache, out, block_table, cu_q, kv_lens, work, nq, nkv,
                                         hd, page_size, scale, window=0, tiles_per_block=2, nsplit=1, kv_chunk=0,
-                                        part_o=None, part_ml=None, sinks=None):
+                                        part_o=None, part_ml=None, sinks=None, mods=None):
         """Rows-split attention on tcgen05 tensor cores with accumulators in tensor memory (head size
         128; page_size 8..64 a power of two, or a multiple of 128); work: int32 [n, 2] (entry, block of
         tiles_per_block x 128 rows), tiles_per_block 1 or 2.  nsplit > 1: the keys in slices of kv_chunk
         (a multiple of 128), a block each, added by a second kernel; part_o float32
         [n * 2 * nkv * nsplit * 128, 128] and part_ml [.., 2] are their workspace."""
         err = self._gemm_state(q.device)[1]
-        if sinks is not None:       # float32 [nq]: one more term exp(sink) in each head's softmax denominator
+        if mods is not None:        # (head_scale, pen_weight, pen_rate), float32 [nq] each or None: see paged_attention_general
+            self._check(self.lib.srlm_paged_attention_prefill_tcgen05_mods(
+                _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
+                C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
+                C.c_int(nq), C.c_int(nkv), C.c_int(hd), C.c_int(page_size), C.c_float(scale), C.c_int(window or 0),
+                C.c_int(tiles_per_block), C.c_int(nsplit), C.c_int(kv_chunk), _ptr(part_o), _ptr(part_ml), _ptr(sinks),
+                _ptr(mods[0]), _ptr(mods[1]), _ptr(mods[2]), _ptr(err), _stream()), "paged_attention_prefill_tcgen05")
+        elif sinks is not None:     # float32 [nq]: one more term exp(sink) in each head's softmax denominator
             self._check(self.lib.srlm_paged_attention_prefill_tcgen05_sinks(
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), C.c_longlong(k_cache.shape[0]), _ptr(block_table),
                 C.c_int(block_table.stride(0)), _ptr(cu_q), _ptr(kv_lens), _ptr(work), C.c_int(work.shape[0]),
@@ -639,13 +646,15 @@ class KernelLibrary:
                 and bool(self.lib.srlm_attention_prefill_tcgen05_takes(C.c_int(hd), C.c_int(page_size))))
 
     def paged_attention(self, ctx, q, k_cache, v_cache, out, block_table, nq, nkv, hd, page_size, scale,
-                        window=0, sinks=None):
+                        window=0, sinks=None, mods=None):
         """The product path's attention over the cache for the batch of ``ctx``: tensor cores for
         bfloat16 (keys-split when every entry is a few rows, rows-split otherwise), float32 FMA for
-        the float32 path.  sinks (float32 [nq]): only where sinks_on_tcgen05 says so; every entry then goes
+        the float32 path.  sinks (float32 [nq]), and mods (head_scale, pen_weight, pen_rate: the per-head score
+        changes of paged_attention_general): only where sinks_on_tcgen05 says so; every entry then goes
         to the rows kernel."""
-        if sinks is not None and not self.sinks_on_tcgen05(ctx, q.dtype, nq, nkv, hd, hd, page_size):
-            raise ShapeError("paged_attention: sinks are served by the tensor-memory rows kernel only")
+        if (sinks is not None or mods is not None) and not self.sinks_on_tcgen05(ctx, q.dtype, nq, nkv, hd, hd, page_size):
+            raise ShapeError("paged_attention: sinks and score changes are served by the tensor-memory rows kernel only")
+        special = sinks is not None or mods is not None
         if q.dtype != torch.bfloat16 or hd % 16 or hd > 256 or self.force_simt_attention:
             self.paged_attention_simt(q, k_cache, v_cache, out, block_table, ctx.entry_of_token, ctx.positions,
                                       nq, nkv, hd, page_size, scale, window)
@@ -696,7 +705,7 @@ class KernelLibrary:
         # the step faster in two launches; 32 requests of 128 to 3,200 tokens, 1.5 % slower.
         short = list(range(head)) + list(range(tail, n))
         enough = self.sm_count(q.device) if self.split_mixed_min_blocks is None else self.split_mixed_min_blocks
-        if sinks is None and self.split_mixed_attention and ctx.max_q_len > 1 and short and len(short) * nkv >= enough:
+        if not special and self.split_mixed_attention and ctx.max_q_len > 1 and short and len(short) * nkv >= enough:
             lens = [ctx.host["kv_lens"][e] for e in short]
             if max(lens) * len(lens) > 1.5 * sum(lens):
                 short = []
@@ -749,7 +758,7 @@ class KernelLibrary:
                 part_ml = ctx.workspace.get("attn.rows_part_ml", slabs, 2, torch.float32, reserve=0)
             self.paged_attention_prefill_tcgen05(q, k_cache, v_cache, out, block_table, ctx.cu_q, ctx.kv_lens, work,
                                                  nq, nkv, hd, page_size, scale, window, tiles, nsplit, chunk, part_o,
-                                                 part_ml, sinks=sinks)
+                                                 part_ml, sinks=sinks, mods=mods)
             return
         tma = (hd in (64, 128) and self.lib.srlm_attention_decode_tma_takes(C.c_int(hd), C.c_int(page_size))
                and not self.force_cp_async_decode)
@@ -1002,9 +1011,10 @@ class KernelLibrary:
             "latent_prefill_attention")
 
     def head_gate(self, x, proj, g_off, out, heads, dv):
-        """out[t, h, :] = x[t, h, :] * sigmoid(proj[t, g_off + h]); x float32; g_off < 0: no gate."""
+        """out[t, h, :] = x[t, h, :] * sigmoid(proj[t, g_off + h]); x float32, or bfloat16 (out may then be x itself);
+        g_off < 0: no gate."""
         self._check(self.lib.srlm_head_gate(
-            _ptr(x), _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), C.c_int(g_off), _ptr(out),
+            _ptr(x), dtype_code(x.dtype), _ptr(proj), dtype_code(proj.dtype), C.c_longlong(proj.stride(0)), C.c_int(g_off), _ptr(out),
             dtype_code(out.dtype), C.c_int(x.shape[0]), C.c_int(heads), C.c_int(dv), _stream()), "head_gate")
 
     # ---- the gated delta rule ------------------------------------------------------------------

@@ -63,11 +63,24 @@ class DistanceAttention(Part):
         T = x.shape[0]
         proj = self.proj(ctx, x, "dist_attn.proj", out_dtype=torch.float32)
         k_pool, v_pool, group = ctx.cache.kv_of_entry(run_step.cache)
-        q = ctx.workspace.get("dist_attn.q", T, s.heads * s.head_dim, torch.float32)
+        # prompts and portions with heads of 128 for keys and values: the framework's tensor-memory kernel, which
+        # takes its queries in bfloat16 and changes a row of scores in registers before the softmax
+        page_size = k_pool.shape[2]
+        on_tcgen05 = (ctx.max_q_len > 4 and s.head_dim == s.v_head_dim
+                      and ops.sinks_on_tcgen05(ctx, ctx.dtype, s.heads, s.kv_heads, s.head_dim, s.v_head_dim, page_size))
+        q = ctx.workspace.get("dist_attn.q", T, s.heads * s.head_dim, ctx.dtype if on_tcgen05 else torch.float32)
         ops.attention_unit_norm_append(proj, s.unit_norm_eps, q, k_pool, v_pool, ctx.kv_slot[group], s.heads,
                                        s.kv_heads, s.head_dim, s.v_head_dim, run_step.writes_cache)
         gated = s.output_gate
         attended = ctx.workspace.get("dist_attn.out", T, s.heads * s.v_head_dim, ctx.dtype)
+        if on_tcgen05:
+            ops.paged_attention(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], s.heads, s.kv_heads,
+                                s.head_dim, page_size, s.softmax_scale, s.window or 0,
+                                mods=(self.temperature, self.penalty[0] if self.penalty else None,
+                                      self.penalty[1] if self.penalty else None))
+            if gated:
+                ops.head_gate(attended, proj, self.gate_offset, attended, s.heads, s.v_head_dim)
+            return self.out(ctx, attended, "dist_attn.o")
         raw = ctx.workspace.get("dist_attn.raw", T, s.heads * s.v_head_dim, torch.float32) if gated else attended
         ops.paged_attention_general(ctx, q, k_pool, v_pool, raw, ctx.block_tables[group], None, s.heads, s.kv_heads,
                                     s.head_dim, s.v_head_dim, s.softmax_scale, s.window or 0,

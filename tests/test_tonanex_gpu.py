@@ -55,6 +55,11 @@ CONFIGS = {
                     attn(heads=4, kv_heads=1, dim=64, vdim=128, window=150),
                     attn(heads=8, kv_heads=8, dim=16, vdim=64, window=None, mlp=moe(experts=4, top=4, ff=16, shared=16))],
                    width=128, vocab=260, softcap=9.0),
+    # heads of 128 for keys and values: prompts and portions run the tensor-memory kernel, which changes a row of
+    # scores in registers; decode steps the mma.sync form
+    "heads128": config([attn(heads=4, kv_heads=2, dim=128, vdim=128, window=100),
+                        attn(heads=2, kv_heads=2, dim=128, vdim=128, window=None, mlp=moe(experts=4, top=2, ff=32, shared=32))],
+                       width=128, vocab=210, softcap=8.0),
     # sizes that are 1, odd or no multiple of 8; a window of one token, a window longer than any request;
     # all experts chosen, one expert of two; no cap on the logits
     "odd": config([attn(heads=3, kv_heads=1, dim=24, vdim=8, window=1, mlp=moe(experts=3, top=3, ff=20, shared=12, limit=1.0)),
@@ -317,7 +322,7 @@ def test_long_decoding(model, dtype):
 def test_a_long_prompt_in_portions(model, dtype):
     """700 tokens in portions of 48: the later portions stand behind hundreds of cached keys, most of them
     behind the window and their pages gone."""
-    if model[0] not in ("wide", "attention", "stack"):
+    if model[0] not in ("wide", "attention", "stack", "heads128"):
         pytest.skip("one configuration of each attention kernel is enough")
     reqs = requests_for(model[2], lens=(700,), seed=6)
     eng = build(model[1], dtype, num_pages=48, page_size=16)
@@ -382,13 +387,15 @@ def test_greedy_generation_through_the_scheduler(model, dtype):
 # ---- mechanisms alone, with inputs made so that a fault shows --------------------------------------------------
 
 class _Ctx:
-    """The fields of a step's context that the attention kernel's wrapper reads."""
+    """The fields of a step's context that the attention kernels' wrappers read."""
     def __init__(self, q_lens, kv_lens, dev):
         self.n_entries, self.max_q_len = len(q_lens), max(q_lens)
         self.cu_q = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=dev)
         self.kv_lens = torch.tensor(kv_lens, dtype=torch.int32, device=dev)
         from safetyraise_lmengine_b200.parts import Workspace
         self.kv_bound, self.workspace = max(kv_lens), Workspace(torch.device(dev), 64)
+        self.host = {"q_lens": list(q_lens), "kv_lens": list(kv_lens), "starts": [k - q for q, k in zip(q_lens, kv_lens)]}
+        self.tables = {}
 
 
 def _paged(keys, page_size, order, dtype, dev, first_kept=0):
@@ -411,7 +418,8 @@ def _paged(keys, page_size, order, dtype, dev, first_kept=0):
 @pytest.mark.parametrize("cache_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("dk,dv,heads,kv_heads,window", [(24, 40, 4, 2, 100), (48, 16, 3, 3, 37), (16, 16, 2, 1, 0),
                                                          (32, 64, 4, 2, 64), (64, 128, 8, 2, 129), (48, 64, 6, 1, 33),
-                                                         (96, 80, 4, 4, 300), (32, 256, 2, 2, 65)])
+                                                         (96, 80, 4, 4, 300), (32, 256, 2, 2, 65), (128, 128, 4, 2, 129),
+                                                         (128, 128, 2, 2, 0)])
 def test_attention_kernel_window_edges_penalty_and_temperature(cache_dtype, dk, dv, heads, kv_heads, window):
     """Queries aimed at one key each: just inside the window, just outside it (where a still heavier key waits),
     far back, at page borders and at position 0.  A window one token off, a lost penalty or temperature or a
@@ -458,6 +466,15 @@ def test_attention_kernel_window_edges_penalty_and_temperature(cache_dtype, dk, 
                                     head_scale=temperature.to(dev), penalty=(weight.to(dev), rate.to(dev)))
         err = (out.cpu().double().view(n, heads, dv) - ref[L - n:]).abs().max() / ref.abs().max()
         assert err < tol, (q_lens, float(err))
+        ctx = _Ctx(q_lens, [L], dev)
+        if cache_dtype == torch.bfloat16 and dk == dv and n > 4 and ops.sinks_on_tcgen05(ctx, cache_dtype, heads, kv_heads, dk, dv, page):
+            # heads of 128: the tensor-memory kernel, queries in bfloat16
+            out16 = torch.zeros(n, heads * dv, dtype=torch.bfloat16, device=dev)
+            ops.paged_attention(ctx, q[L - n:].reshape(n, -1).contiguous().to(dev).bfloat16(), k_pool, v_pool, out16, table,
+                                heads, kv_heads, dk, page, scale, window,
+                                mods=(temperature.to(dev), weight.to(dev), rate.to(dev)))
+            err = (out16.cpu().double().view(n, heads, dv) - ref[L - n:]).abs().max() / ref.abs().max()
+            assert err < tol, ("tensor memory", q_lens, float(err))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
