@@ -224,6 +224,12 @@ struct GemmArgs {
                            //    the first sk_blocks blocks, or pairs of blocks (0: every block takes whole tiles only)
   int m_major;             // persistent kernel: tile t covers token tile t / (tiles along N); else t % (tiles along M)
   GemmFuse fuse;           // one-tile kernel only; all zero: none
+  // persistent kernel, one SM per tile: grouped products.  Token tile mt (128 rows) multiplies the weight rows
+  // [group_of_mtile[mt] * N, + N) of W (N: weight rows per group); a tile whose entry is negative is skipped.
+  const int* group_of_mtile = nullptr;
+  // swiglu8 with glu_limit > 0: the output is g * logistic(glu_alpha * g) * (u + 1), g = min(gate, limit),
+  // u = clamp(up, -limit, limit), instead of silu(gate) * up
+  float glu_limit = 0.f, glu_alpha = 0.f;
 };
 
 __device__ __forceinline__ void cluster_sync_all() {   // every thread of every block of the cluster
@@ -763,6 +769,13 @@ __device__ __forceinline__ void acc_drained(uint64_t* bar) {
   else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// g * logistic(alpha * g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); fast exponential and
+// reciprocal as in silu_stable (exp2 of a large argument is +inf, its reciprocal 0)
+__device__ __forceinline__ float clamped_glu_fast(float gate, float up, float limit, float alpha) {
+  const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+  return g * __frcp_rn(1.f + exp2f(-alpha * 1.4426950408889634f * g)) * (u + 1.f);
+}
+
 template <int BN, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -830,7 +843,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
       int t, kb_lo, kb_hi;
       while (ok && walk.next(t, kb_lo, kb_hi)) {
         const int m0 = (args.m_major ? t / tiles_n : t % tiles_m) * BN + (int)rank * (PAIR ? B_ROWS : 0);
-        const int n0 = (args.m_major ? t % tiles_n : t / tiles_m) * TILE_N + (int)rank * BM;
+        int n0 = (args.m_major ? t % tiles_n : t / tiles_m) * TILE_N + (int)rank * BM;
+        if (args.group_of_mtile) {
+          const int grp = args.group_of_mtile[args.m_major ? t / tiles_n : t % tiles_m];
+          if (grp < 0) continue;                          // no rows in this token tile: every role skips it
+          n0 += grp * args.N;                             // the group's rows of the stacked weights
+        }
         for (int kb = kb_lo; kb < kb_hi; ++kb, ++it) {
           const int s = it % STAGES, j = it / STAGES;
           ok = mbar_wait(&empty_bar[s], (j & 1) ^ 1, args.err_flag, 21);
@@ -858,7 +876,12 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
       bool ok = true;
       PieceWalk walk(args, num_kb, total_tiles, walker, walkers);
       int t, kb_lo, kb_hi;
+      if (args.group_of_mtile) pdl_wait();                 // the table is written by a kernel of the same step
       for (; ok && walk.next(t, kb_lo, kb_hi); ++local) {
+        if (args.group_of_mtile && args.group_of_mtile[args.m_major ? t / tiles_n : t % tiles_m] < 0) {
+          --local;
+          continue;
+        }
         const int b = local & 1;
         ok = mbar_wait(&acc_empty[b], ((local >> 1) & 1) ^ 1, args.err_flag, 22);   // epilogue has drained it
         if (!ok) break;
@@ -902,6 +925,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
     const int slot_block = (int)blockIdx.x;
     constexpr size_t SLOT = (size_t)BN * BM;                // floats of a slot: [BN tokens][128 weight rows]
     for (; ok && walk.next(t, kb_lo, kb_hi); ++local) {
+      if (args.group_of_mtile && args.group_of_mtile[args.m_major ? t / tiles_n : t % tiles_m] < 0) {
+        --local;
+        continue;
+      }
       const int b = local & 1;
       const int m0 = (args.m_major ? t / tiles_n : t % tiles_m) * BN;
       const int n0 = (args.m_major ? t % tiles_n : t / tiles_m) * TILE_N + (int)rank * BM;
@@ -1064,7 +1091,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const 
           for (int j = 0; j < SLAB; j += 2) {
             const float mine0 = __uint_as_float(v[j]), mine1 = __uint_as_float(v[j + 1]);
             const float got = __shfl_xor_sync(0xffffffffu, gate_lane ? mine1 : mine0, 8);
-            const float hval = gate_lane ? silu_stable(mine0) * got : silu_stable(got) * mine1;
+            const float gv = gate_lane ? mine0 : got, uv = gate_lane ? got : mine1;
+            const float hval = args.glu_limit > 0.f ? clamped_glu_fast(gv, uv, args.glu_limit, args.glu_alpha)
+                                                    : silu_stable(gv) * uv;
             const int row = gate_lane ? j : j + 1;
             if (args.c_is_f32) *reinterpret_cast<float*>(sl + row * SLAB_ROW + col * 4) = hval;
             else *reinterpret_cast<bf16*>(sl + row * SLAB_ROW + col * 2) = __float2bfloat16_rn(hval);
@@ -1603,4 +1632,30 @@ extern "C" int srlm_gemm_tn_tcgen05_static(const void* X, const void* W, void* C
   if (e == cudaSuccess) e = cudaMemcpy(err_flag_out, err, sizeof(int), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return refuse((int)e, "gemm_static: reading the error flag: %s", cudaGetErrorString(e));
   return ST_OK;
+}
+
+// Grouped products on the persistent kernel: token tile mt of X (128 rows; X and C hold every group's rows from a
+// multiple of 128 on) multiplies the N weight rows of group group_of_mtile[mt] (device, int32 [ceil(M / 128)];
+// negative: the tile is skipped and its rows of C are not written).  W: [groups * N, K], contiguous.  glu: the
+// weight rows of a group come in blocks of 16 (8 gate rows, then the 8 up rows of the same features) and
+// C [M, N / 2] gets g * logistic(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
+extern "C" int srlm_gemm_tn_tcgen05_grouped(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                            long long ldx, long long ldc, int groups, const int* group_of_mtile, int glu,
+                                            float limit, float alpha, int* err_flag, cudaStream_t stream) {
+  if (M <= 0) return ST_OK;
+  if (N <= 0 || K <= 0 || groups <= 0 || !group_of_mtile || ldx < K || ldc < (glu ? N / 2 : N) || (glu && (N % 16 || !(limit > 0.f))))
+    return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: M=%d N=%d K=%d groups=%d ldx=%lld ldc=%lld glu=%d", M, N, K, groups, ldx,
+                  ldc, glu);
+  if (K % 8 || ldx % 8) return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: K=%d and ldx must be multiples of 8", K);
+  if (((uintptr_t)X | (uintptr_t)W) & 15) return refuse(ST_BAD_ALIGN, "gemm_tcgen05_grouped: operands must be 16-byte aligned");
+  if (c_dtype != DT_F32 && c_dtype != DT_BF16) return refuse(ST_BAD_DTYPE, "gemm_tcgen05_grouped: output dtype %d", c_dtype);
+  GemmArgs a{C, c_dtype == DT_F32, M, N, K, ldc, err_flag, (K + BK - 1) / BK, nullptr, nullptr, glu ? 1 : 0, 0};
+  a.group_of_mtile = group_of_mtile;
+  a.glu_limit = glu ? limit : 0.f;
+  a.glu_alpha = alpha;
+  CUtensorMap mw_copy, mx_copy;
+  const CUtensorMap *mw = &mw_copy, *mx = &mx_copy;
+  if (!cached_map(&mw_copy, W, (long long)groups * N, K, K, BM, true) || !cached_map(&mx_copy, X, M, K, ldx, 128, false))
+    return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: cuTensorMapEncodeTiled refused the operands");
+  return launch_persistent<128, 5>(mw, mx, a, 0, stream);
 }

@@ -73,16 +73,24 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
 }
 
 // One block.  offsets[E + 1]: first row of each expert; tiles[E + 1]: first tile of each expert (tiles of
-// kTile rows, none shared by two experts); pair_of_row[n]; row_of_pair[n].  Which row of its expert a pair
+// tile_rows rows, none shared by two experts); pair_of_row[n]; row_of_pair[n].  Which row of its expert a pair
 // gets depends on the order the threads arrive in; no result depends on it.
-__global__ void moe_sort_kernel(const int* __restrict__ choice, int n, int E, int* __restrict__ offsets,
-                                int* __restrict__ tiles, int* __restrict__ pair_of_row, int* __restrict__ row_of_pair) {
+// align: every expert's rows start at a multiple of tile_rows (for products whose tiles are fixed rows of their
+// operands); pair_of_row then has rows_cap entries, -1 where a row holds no pair, and group_of_tile[max_tiles]
+// names the expert of every tile, -1 for a tile without rows.
+__global__ void moe_sort_kernel(const int* __restrict__ choice, int n, int E, int tile_rows, int align,
+                                int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ pair_of_row,
+                                int* __restrict__ row_of_pair, int* __restrict__ group_of_tile, int max_tiles, int rows_cap) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ int sort_smem[];
   int* count = sort_smem;            // [E]
   int* start = count + E;            // [E + 1]
   for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  if (align) {
+    for (int i = threadIdx.x; i < rows_cap; i += blockDim.x) pair_of_row[i] = -1;
+    for (int i = threadIdx.x; i < max_tiles; i += blockDim.x) group_of_tile[i] = -1;
+  }
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const int e = choice[i];
@@ -92,11 +100,15 @@ __global__ void moe_sort_kernel(const int* __restrict__ choice, int n, int E, in
   if (threadIdx.x == 0) {
     int rows = 0, tl = 0;
     for (int e = 0; e < E; ++e) {
+      if (align) rows = tl * tile_rows;
       start[e] = rows;
       offsets[e] = rows;
       tiles[e] = tl;
       rows += count[e];
-      tl += (count[e] + kTile - 1) / kTile;
+      const int nt = (count[e] + tile_rows - 1) / tile_rows;
+      if (align)
+        for (int i = tl; i < tl + nt && i < max_tiles; ++i) group_of_tile[i] = e;
+      tl += nt;
     }
     start[E] = rows;
     offsets[E] = rows;
@@ -111,6 +123,22 @@ __global__ void moe_sort_kernel(const int* __restrict__ choice, int n, int E, in
     const int row = start[e] + atomicAdd(&count[e], 1);
     pair_of_row[row] = i;
     row_of_pair[i] = row;
+  }
+}
+
+// xs[row, :] = x[pair_of_row[row] / pairs_per_token, :], zeros for a row without a pair; 16 bytes a thread
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ x, long long ldx, const int* __restrict__ pair_of_row,
+                                       int pairs_per_token, bf16* __restrict__ xs, int rows, int K) {
+  pdl_wait();
+  pdl_trigger();
+  const int vecs = K / 8;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < (long long)rows * vecs;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(idx / vecs), c = (int)(idx - (long long)row * vecs);
+    const int pair = pair_of_row[row];
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (pair >= 0) v = *reinterpret_cast<const uint4*>(x + (size_t)(pair / pairs_per_token) * ldx + c * 8);
+    *reinterpret_cast<uint4*>(xs + (size_t)row * K + c * 8) = v;
   }
 }
 
@@ -384,12 +412,34 @@ extern "C" int srlm_moe_route(const float* logits, long long ld, const float* bi
 }
 
 // choice int32 [n] (n = tokens x top); offsets, tiles int32 [E + 1]; pair_of_row, row_of_pair int32 [n]
+// tile_rows 0: the tiles of the grouped kernels of this file, rows packed.  tile_rows > 0: every expert's rows
+// start at a multiple of it; group_of_tile [max_tiles >= (n + E * (tile_rows - 1)) / tile_rows] names each tile's
+// expert (-1: none) and pair_of_row has rows_cap >= max_tiles * tile_rows entries (-1: no pair).
 extern "C" int srlm_moe_sort(const int* choice, int n, int E, int* offsets, int* tiles, int* pair_of_row,
-                             int* row_of_pair, cudaStream_t stream) {
+                             int* row_of_pair, int tile_rows, int* group_of_tile, int max_tiles, int rows_cap,
+                             cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (E <= 0 || E > 4096) return refuse(ST_BAD_SIZE, "moe_sort: experts=%d (at most 4096)", E);
-  launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, choice, n, E, offsets, tiles,
-             pair_of_row, row_of_pair);
+  const int align = tile_rows > 0;
+  if (align && (!group_of_tile || (long long)max_tiles < ((long long)n + (long long)E * (tile_rows - 1)) / tile_rows ||
+                rows_cap < max_tiles * tile_rows))
+    return refuse(ST_BAD_SIZE, "moe_sort: %d pairs over %d experts in tiles of %d need more than %d tiles, %d rows", n, E,
+                  tile_rows, max_tiles, rows_cap);
+  launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, choice, n, E,
+             align ? tile_rows : kTile, align, offsets, tiles, pair_of_row, row_of_pair, group_of_tile, max_tiles, rows_cap);
+  return launched();
+}
+
+// xs [rows, K] bfloat16 = the rows of x [tokens, ldx] that pair_of_row names (pair / pairs_per_token), zeros for -1
+extern "C" int srlm_moe_gather_rows(const void* x, long long ldx, const int* pair_of_row, int pairs_per_token, void* xs,
+                                    int rows, int K, cudaStream_t stream) {
+  if (rows <= 0) return ST_OK;
+  if (K <= 0 || K % 8 || ldx % 8 || pairs_per_token <= 0 || ((((uintptr_t)x | (uintptr_t)xs) & 15) != 0))
+    return refuse(ST_BAD_SIZE, "moe_gather_rows: K=%d ldx=%lld (multiples of 8, 16-byte aligned)", K, ldx);
+  const long long total = (long long)rows * (K / 8);
+  long long g = (total + 255) / 256;
+  launch_pdl(moe_gather_rows_kernel, dim3((unsigned)(g > 148 * 16 ? 148 * 16 : g)), dim3(256), 0, stream, (const bf16*)x, ldx,
+             pair_of_row, pairs_per_token, (bf16*)xs, rows, K);
   return launched();
 }
 

@@ -75,6 +75,7 @@ class KernelLibrary:
         self.latent_prompts_in_head_space = True        # latent attention: prompts form per-head keys and values
         self.sinks_in_tcgen05_prefill = True            # attention with sinks, heads of 128: prompts on the tcgen05 kernel
         self.grouped_products_on_tensor_cores = True    # routed experts in bfloat16: mma.sync, when the sizes fit
+        self.grouped_products_in_tensor_memory = True   # ... and steps of many tokens: the persistent tcgen05 kernel
 
     @property
     def lib(self):
@@ -907,11 +908,38 @@ class KernelLibrary:
         self._check(self.lib.srlm_moe_route(_ptr(logits), C.c_longlong(logits.stride(0)), _ptr(bias), C.c_int(T), C.c_int(E),
                                             C.c_int(top), _ptr(choice), _ptr(weight), _stream()), "moe_route")
 
-    def moe_sort(self, choice, experts, offsets, tiles, pair_of_row, row_of_pair):
+    def moe_sort(self, choice, experts, offsets, tiles, pair_of_row, row_of_pair, tile_rows=0, group_of_tile=None):
         """The (token, choice) pairs ordered by expert: offsets / tiles int32 [experts + 1] (first row and first
-        tile of each expert), pair_of_row / row_of_pair int32 [pairs]."""
-        self._check(self.lib.srlm_moe_sort(_ptr(choice), C.c_int(choice.numel()), C.c_int(experts), _ptr(offsets),
-                                           _ptr(tiles), _ptr(pair_of_row), _ptr(row_of_pair), _stream()), "moe_sort")
+        tile of each expert), pair_of_row / row_of_pair int32 [pairs].  tile_rows > 0: every expert's rows start at
+        a multiple of tile_rows; pair_of_row then covers all rows of group_of_tile's tiles (-1: a row without a
+        pair) and group_of_tile int32 [tiles] names each tile's expert (-1: none)."""
+        self._check(self.lib.srlm_moe_sort(
+            _ptr(choice), C.c_int(choice.numel()), C.c_int(experts), _ptr(offsets), _ptr(tiles), _ptr(pair_of_row),
+            _ptr(row_of_pair), C.c_int(tile_rows), _ptr(group_of_tile),
+            C.c_int(group_of_tile.numel() if group_of_tile is not None else 0),
+            C.c_int(pair_of_row.numel()), _stream()), "moe_sort")
+
+    GROUPED_TILE = 128       # token rows of a tile of the grouped tensor-memory product
+
+    def moe_gather_rows(self, x, pair_of_row, pairs_per_token, out):
+        """out[row] = x[pair_of_row[row] // pairs_per_token] (bfloat16 rows; zeros where pair_of_row is -1)."""
+        self._check(self.lib.srlm_moe_gather_rows(_ptr(x), C.c_longlong(x.stride(0)), _ptr(pair_of_row),
+                                                  C.c_int(pairs_per_token), _ptr(out), C.c_int(out.shape[0]),
+                                                  C.c_int(out.shape[1]), _stream()), "moe_gather_rows")
+
+    def gemm_tn_tcgen05_grouped(self, x, w, out, group_of_tile, glu=False, limit=0.0, alpha=0.0):
+        """out[r] = x[r] . w[group of r's tile]^T on the persistent tensor-memory kernel: x [rows, K] bfloat16 in tiles
+        of 128 rows, w [groups, N, K]; a tile whose group is negative is skipped.  glu: w's rows in blocks of 8 gate
+        and 8 up rows, out [rows, N / 2] = the clamped GLU."""
+        rows, K = x.shape
+        G, N, _ = w.shape
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[2] != K or group_of_tile.numel() * 128 < rows:
+            raise ShapeError(f"gemm_tcgen05_grouped: x {tuple(x.shape)}, w {tuple(w.shape)}, {group_of_tile.numel()} tiles")
+        err = self._gemm_state(x.device)[1]
+        self._check(self.lib.srlm_gemm_tn_tcgen05_grouped(
+            _ptr(x), _ptr(w), _ptr(out), dtype_code(out.dtype), C.c_int(rows), C.c_int(N), C.c_int(K),
+            C.c_longlong(x.stride(0)), C.c_longlong(out.stride(0)), C.c_int(G), _ptr(group_of_tile), C.c_int(int(glu)),
+            C.c_float(limit), C.c_float(alpha), _ptr(err), _stream()), "gemm_tn_tcgen05_grouped")
 
     def moe_grouped(self, a, pair_of_row, pairs_per_token, w, out, offsets, tiles, glu=False, interleaved=False,
                     limit=0.0, alpha=0.0):

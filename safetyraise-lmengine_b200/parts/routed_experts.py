@@ -81,6 +81,11 @@ class RoutedExperts(Part):
         choice = ws.get("moe.choice", T, s.top, torch.int32)
         weight = ws.get("moe.weight", T, s.top, torch.float32)
         ops.moe_route(logits, self.router_bias, s.top, choice, weight)
+        # steps of many tokens (64 rows an expert on average): the experts' products on the persistent tensor-memory
+        # kernel, every expert's rows in whole tiles of 128 of a gathered copy of the input
+        if (self.interleaved and ops.grouped_products_in_tensor_memory and pairs >= 64 * s.experts
+                and s.intermediate_size % 8 == 0):
+            return self._forward_tiles(ctx, x, choice, weight)
         heads = ws.get("moe.heads", 2, s.experts + 1, torch.int32, reserve=2)
         order = ws.get("moe.order", 2 * T, s.top, torch.int32, reserve=2 * ws.max_tokens)
         offsets, tiles = heads[0], heads[1]
@@ -91,12 +96,39 @@ class RoutedExperts(Part):
                         limit=s.limit, alpha=s.glu_alpha)
         rows = ws.get("moe.rows", pairs, H, torch.float32, reserve=ws.max_tokens * s.top)
         ops.moe_grouped(y, None, 1, self.down, rows, offsets, tiles)
-        shared = None
-        if self.shared_gate_up is not None:
-            gu = self.shared_gate_up(ctx, x, "moe.shared_gu", out_dtype=torch.float32)
-            ys = ws.get("moe.shared_y", T, s.shared_size, ctx.dtype)
-            ops.clamped_glu(gu, ys, s.shared_limit, s.glu_alpha)
-            shared = self.shared_down(ctx, ys, "moe.shared_out")
         out = ws.get("moe.out", T, H, ctx.dtype)
-        ops.moe_combine(rows, row_of_pair, weight, shared, out)
+        ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, x), out)
+        return out
+
+    def _shared(self, ctx, x):
+        """The output of the expert that every token runs, or None."""
+        if self.shared_gate_up is None:
+            return None
+        s = self.spec
+        gu = self.shared_gate_up(ctx, x, "moe.shared_gu", out_dtype=torch.float32)
+        ys = ctx.workspace.get("moe.shared_y", x.shape[0], s.shared_size, ctx.dtype)
+        ops.clamped_glu(gu, ys, s.shared_limit, s.glu_alpha)
+        return self.shared_down(ctx, ys, "moe.shared_out")
+
+    def _forward_tiles(self, ctx, x, choice, weight):
+        s = self.spec
+        T, H = x.shape
+        ws = ctx.workspace
+        tile = ops.GROUPED_TILE
+        n_tiles = (T * s.top) // tile + s.experts            # every expert wastes less than one tile
+        rows_cap = n_tiles * tile
+        heads = ws.get("moe.heads", 2, s.experts + 1, torch.int32, reserve=2)
+        group_of_tile = ws.get("moe.group_of_tile", n_tiles, 1, torch.int32, reserve=0).view(-1)
+        pair_of_row = ws.get("moe.pair_of_row", rows_cap, 1, torch.int32, reserve=0).view(-1)
+        row_of_pair = ws.get("moe.row_of_pair", T, s.top, torch.int32).view(-1)
+        ops.moe_sort(choice, s.experts, heads[0], heads[1], pair_of_row, row_of_pair, tile_rows=tile,
+                     group_of_tile=group_of_tile)
+        xs = ws.get("moe.xs", rows_cap, H, ctx.dtype, reserve=0)
+        ops.moe_gather_rows(x, pair_of_row, s.top, xs)
+        y = ws.get("moe.y_tiles", rows_cap, s.intermediate_size, ctx.dtype, reserve=0)
+        ops.gemm_tn_tcgen05_grouped(xs, self.gate_up, y, group_of_tile, glu=True, limit=s.limit, alpha=s.glu_alpha)
+        rows = ws.get("moe.rows_tiles", rows_cap, H, torch.float32, reserve=0)
+        ops.gemm_tn_tcgen05_grouped(y, self.down, rows, group_of_tile)
+        out = ws.get("moe.out", T, H, ctx.dtype)
+        ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, x), out)
         return out

@@ -140,8 +140,8 @@ def plain(name, cfg, W, tokens):
 def build(folder, dtype, num_pages=64, page_size=16, **kw):
     from safetyraise_lmengine_b200 import Engine
     kw.setdefault("max_context", 1024)
-    return Engine.from_folder(folder, dtype=dtype, page_size=page_size, num_pages=num_pages, max_requests=4,
-                              max_batch_tokens=512, **kw)
+    kw.setdefault("max_batch_tokens", 512)
+    return Engine.from_folder(folder, dtype=dtype, page_size=page_size, num_pages=num_pages, max_requests=4, **kw)
 
 
 def check(got, model, requests, dtype):
@@ -328,6 +328,18 @@ def test_a_long_prompt_in_portions(model, dtype):
     eng = build(model[1], dtype, num_pages=48, page_size=16)
     got = replay(eng, cut_portions("r0", reqs["r0"], sizes=(48,)))
     check(got, model, reqs, dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_long_prompt_in_one_step(model, dtype):
+    """900 tokens at once, beside a short request: steps of many tokens run the experts' products in whole tiles on
+    the tensor-memory kernel (bfloat16), and the attention's row tiles stand behind hundreds of keys of their own step."""
+    reqs = requests_for(model[2], lens=(900, 40), seed=8)
+    eng = build(model[1], dtype, num_pages=72, page_size=16, max_batch_tokens=1024)
+    got = replay(eng, [{"entries": [("r1", reqs["r1"], list(range(40))), ("r0", reqs["r0"], list(range(900)))],
+                        "end": ["r0", "r1"]}])
+    check(got, model, reqs, dtype)
+    assert all_pages_free(eng, 72)
 
 
 def test_cuttings_agree_bit_for_bit_in_float32(model):
@@ -566,6 +578,58 @@ def test_grouped_products_of_the_experts(dtype, interleaved):
                 want[t] += weight[t, c].double() * P.expert(x[t:t + 1], W, "", 1.2)[0]
         err = (out.cpu().double() - want).abs().max() / want.abs().max()
         assert err < (2e-5 if dtype == torch.float32 else 2e-2), (T, E, top, float(err))
+
+
+def test_grouped_products_in_tiles_of_tensor_memory():
+    """Steps of many tokens: every expert's rows in whole tiles of 128 of a gathered copy, both products on the
+    persistent tensor-memory kernel.  An expert nobody chose, one with a single row, one with several tiles."""
+    from safetyraise_lmengine_b200.kernels import ops
+    dev = "cuda:0"
+    g = torch.Generator().manual_seed(14)
+    for T, E, top, H, ff in ((700, 5, 2, 64, 48), (130, 3, 1, 136, 200), (512, 4, 4, 256, 128)):
+        x = torch.randn(T, H, generator=g).bfloat16()
+        gu = (0.4 * torch.randn(E, 2 * ff, H, generator=g)).bfloat16()
+        dn = (0.3 * torch.randn(E, H, ff, generator=g)).bfloat16()
+        choice = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(T)]).to(torch.int32)
+        if E == 5:
+            choice[choice == 3] = 0
+            choice[:, 1] = torch.where(choice[:, 0] == 4, 1, 4)
+            choice[7, 0] = 2
+            choice[choice[:, 0] == 2, 0] = 0
+            choice[7, 0] = 2                                    # expert 2: one row; expert 3: none; expert 4: many tiles
+        weight = torch.rand(T, top, generator=g)
+        n, tile = T * top, ops.GROUPED_TILE
+        n_tiles = n // tile + E
+        d = lambda t: t.to(dev)
+        heads = torch.zeros(2, E + 1, dtype=torch.int32, device=dev)
+        got = torch.full((n_tiles,), -7, dtype=torch.int32, device=dev)
+        por = torch.full((n_tiles * tile,), -7, dtype=torch.int32, device=dev)
+        rop = torch.zeros(n, dtype=torch.int32, device=dev)
+        ops.moe_sort(d(choice), E, heads[0], heads[1], por, rop, tile_rows=tile, group_of_tile=got)
+        counts = [int((choice == e).sum()) for e in range(E)]
+        assert all(int(heads[0][e]) % tile == 0 for e in range(E))
+        want_groups = sum(([e] * -(-c // tile) for e, c in enumerate(counts)), [])
+        assert got.tolist() == want_groups + [-1] * (n_tiles - len(want_groups))
+        assert all(int(por[int(rop[i])]) == i for i in range(n)) and int((por >= 0).sum()) == n
+        gu_dev = torch.stack([d(gu)[:, :ff].reshape(E, ff // 8, 8, H), d(gu)[:, ff:].reshape(E, ff // 8, 8, H)],
+                             dim=2).reshape(E, 2 * ff, H).contiguous()
+        xs = torch.empty(n_tiles * tile, H, dtype=torch.bfloat16, device=dev)
+        ops.moe_gather_rows(d(x), por, top, xs)
+        y = torch.zeros(n_tiles * tile, ff, dtype=torch.bfloat16, device=dev)
+        ops.gemm_tn_tcgen05_grouped(xs, gu_dev, y, got, glu=True, limit=1.2, alpha=1.702)
+        rows = torch.zeros(n_tiles * tile, H, device=dev)
+        ops.gemm_tn_tcgen05_grouped(y, d(dn), rows, got)
+        out = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+        ops.moe_combine(rows, rop, d(weight), None, out)
+        assert ops.gemm_error_flag(torch.device(dev)) == 0
+        want = torch.zeros(T, H, dtype=torch.float64)
+        for t in range(T):
+            for c in range(top):
+                e = int(choice[t, c])
+                W = {"gate": gu[e, :ff], "up": gu[e, ff:], "down": dn[e]}
+                want[t] += weight[t, c].double() * P.expert(x[t:t + 1], W, "", 1.2)[0]
+        err = (out.cpu().double() - want).abs().max() / want.abs().max()
+        assert err < 2e-2, (T, E, top, float(err))
 
 
 def test_cap_and_clamped_activation():
