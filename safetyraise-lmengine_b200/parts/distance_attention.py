@@ -58,10 +58,25 @@ class DistanceAttention(Part):
         return CacheNeed(PAGED_WINDOW if s.window else PAGED_ALL, s.kv_heads, s.head_dim, s.window,
                          v_head_dim=None if s.v_head_dim == s.head_dim else s.v_head_dim)
 
+    def can_fuse(self, ctx) -> bool:
+        return self.proj.can_fuse(ctx, ctx.T) and self.out.can_fuse(ctx, ctx.T)
+
+    def forward_fused(self, ctx, nx, run_step: RunStep, residual: torch.Tensor, next_norm):
+        """The same as forward for a lazily normalised input (the norm's scale is applied inside the stacked
+        product), with the output projection adding into the residual stream and preparing the input of the
+        part behind ``next_norm``."""
+        proj = ctx.workspace.get("dist_attn.proj", ctx.T, self.proj.out_features, torch.float32)
+        self.proj.from_normed(ctx, nx, proj)
+        return self.out.into_residual(ctx, self._attend(ctx, proj, run_step), residual, next_norm, "a", early=False)
+
     def forward(self, ctx, x: torch.Tensor, run_step: RunStep) -> torch.Tensor:
-        s = self.spec
-        T = x.shape[0]
         proj = self.proj(ctx, x, "dist_attn.proj", out_dtype=torch.float32)
+        return self.out(ctx, self._attend(ctx, proj, run_step), "dist_attn.o")
+
+    def _attend(self, ctx, proj: torch.Tensor, run_step: RunStep) -> torch.Tensor:
+        """From the stacked projection to the gated heads' outputs [T, heads * v_head_dim]."""
+        s = self.spec
+        T = proj.shape[0]
         k_pool, v_pool, group = ctx.cache.kv_of_entry(run_step.cache)
         # prompts and portions with heads of 128 for keys and values: the framework's tensor-memory kernel, which
         # takes its queries in bfloat16 and changes a row of scores in registers before the softmax
@@ -80,11 +95,11 @@ class DistanceAttention(Part):
                                       self.penalty[1] if self.penalty else None))
             if gated:
                 ops.head_gate(attended, proj, self.gate_offset, attended, s.heads, s.v_head_dim)
-            return self.out(ctx, attended, "dist_attn.o")
+            return attended
         raw = ctx.workspace.get("dist_attn.raw", T, s.heads * s.v_head_dim, torch.float32) if gated else attended
         ops.paged_attention_general(ctx, q, k_pool, v_pool, raw, ctx.block_tables[group], None, s.heads, s.kv_heads,
                                     s.head_dim, s.v_head_dim, s.softmax_scale, s.window or 0,
                                     head_scale=self.temperature, penalty=self.penalty)
         if gated:
             ops.head_gate(raw, proj, self.gate_offset, attended, s.heads, s.v_head_dim)
-        return self.out(ctx, attended, "dist_attn.o")
+        return attended
