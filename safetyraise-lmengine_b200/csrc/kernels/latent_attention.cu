@@ -212,6 +212,29 @@ __global__ void head_gate_kernel(const TI* in, const TP* __restrict__ proj, long
   }
 }
 
+// The same for bfloat16 rows whose heads are whole 16-byte pieces (dv a multiple of 8): a thread takes eight elements.
+template <typename TP>
+__global__ void head_gate_vec_kernel(const bf16* in, const TP* __restrict__ proj, long long ldp, int g_off, bf16* out,
+                                     int heads, int dv, long long pieces) {
+  pdl_wait();
+  pdl_trigger();
+  const int per_row = heads * dv / 8;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < pieces;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / per_row;
+    const int c = (int)(idx - t * per_row) * 8;
+    const float g = 1.f / (1.f + expf(-to_float(proj[(size_t)t * ldp + g_off + c / dv])));
+    uint4 v = *reinterpret_cast<const uint4*>(in + (size_t)t * heads * dv + c);
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      h[i] = __floats2bfloat162_rn(f.x * g, f.y * g);
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * heads * dv + c) = v;
+  }
+}
+
 }  // namespace srlm
 
 using namespace srlm;
@@ -304,6 +327,16 @@ extern "C" int srlm_head_gate(const void* in, int in_dtype, const void* proj, in
   if (T <= 0) return ST_OK;
   if (heads <= 0 || dv <= 0 || (g_off >= 0 && ldp < g_off + heads))
     return refuse(ST_BAD_SIZE, "head_gate: heads=%d dv=%d g_off=%d ldp=%lld", heads, dv, g_off, ldp);
+  if (in_dtype == DT_BF16 && out_dtype == DT_BF16 && g_off >= 0 && dv % 8 == 0 && ((((uintptr_t)in | (uintptr_t)out) & 15) == 0)) {
+    const long long pieces = (long long)T * heads * dv / 8;
+    const long long g = (pieces + 255) / 256;
+    const dim3 grid((unsigned)(g > 148 * 16 ? 148 * 16 : g));
+    if (proj_dtype == DT_F32)
+      launch_pdl(head_gate_vec_kernel<float>, grid, dim3(256), 0, stream, (const bf16*)in, (const float*)proj, ldp, g_off, (bf16*)out, heads, dv, pieces);
+    else
+      launch_pdl(head_gate_vec_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)in, (const bf16*)proj, ldp, g_off, (bf16*)out, heads, dv, pieces);
+    return launched();
+  }
 #define SRLM_GATE(TI, TP, TA) launch_pdl(head_gate_kernel<TI, TP, TA>, dim3(T), dim3(256), 0, stream, (const TI*)in, (const TP*)proj, ldp, g_off, (TA*)out, heads, dv)
   if (in_dtype == DT_F32 && proj_dtype == DT_F32 && out_dtype == DT_F32) SRLM_GATE(float, float, float);
   else if (in_dtype == DT_F32 && proj_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_GATE(float, float, bf16);
