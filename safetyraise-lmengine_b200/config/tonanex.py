@@ -90,27 +90,40 @@ def read_spec(root: dict) -> ModelSpec:
     if not isinstance(entries, list) or not entries or len(entries) > MAX_LAYERS:
         raise ConfigError(f"config.json: 'layers' must list 1 to {MAX_LAYERS} layers")
     norm = NormSpec("rmsnorm", width, eps)
-    layers, index_of, run_order = [], {}, []
+    parsed = []
     for i, entry in enumerate(entries):
         where = f"layers[{i}]."
         if not isinstance(entry, dict) or not isinstance(entry.get("type"), str):
             raise ConfigError(f"config.json: {where[:-1]} must be an object with a 'type'")
         mixer = _mixer(entry["type"], _obj(entry, "mixer", where), width, eps, where + "mixer.")
         ff = _feed_forward(_obj(entry, "mlp", where), width, where + "mlp.") if entry.get("mlp") is not None else None
-        if "weights_of" in entry:
-            j = entry["weights_of"]
-            if isinstance(j, bool) or not isinstance(j, int) or not 0 <= j < i:
-                raise ConfigError(f"config.json: {where}'weights_of' must name an earlier layer, got {j!r}")
-            owner = layers[index_of[j]]          # index_of follows a chain of borrowers to the layer that owns
-            if (mixer, ff) != (owner.mixer, owner.feed_forward):
-                raise ConfigError(f"config.json: {where[:-1]} runs the weights of layer {j} but differs from it")
-            index_of[i] = index_of[j]
-        else:
+        j = entry.get("weights_of")
+        if "weights_of" in entry and (isinstance(j, bool) or not isinstance(j, int) or not 0 <= j < len(entries) or j == i):
+            raise ConfigError(f"config.json: {where}'weights_of' must name another layer, got {j!r}")
+        parsed.append((mixer, ff, j if "weights_of" in entry else None))
+
+    def owner_of(i: int) -> int:
+        """The layer whose tensors layer i runs: a chain of borrowers ends at a layer with tensors of its own."""
+        seen = set()
+        while parsed[i][2] is not None:
+            if i in seen:
+                raise ConfigError(f"config.json: layers[{i}].weights_of leads back to itself")
+            seen.add(i)
+            i = parsed[i][2]
+        return i
+
+    layers, index_of, run_order = [], {}, []
+    for i, (mixer, ff, _) in enumerate(parsed):      # the layers that own tensors, in their order
+        if parsed[i][2] is None:
             index_of[i] = len(layers)
             layers.append(LayerSpec(block="pre_norm", mixer=mixer, feed_forward=ff, mixer_norm=norm,
                                     feed_forward_norm=norm if ff else None, weight_prefix=f"l{i}.",
                                     mixer_norm_name="norm1", feed_forward_norm_name="norm2"))
-        run_order.append(RunStep(index_of[i], i, True))      # every run has a cache entry of its own
+    for i, (mixer, ff, j) in enumerate(parsed):
+        owner = owner_of(i)
+        if (mixer, ff) != parsed[owner][:2]:
+            raise ConfigError(f"config.json: layers[{i}] runs the weights of layer {owner} but differs from it")
+        run_order.append(RunStep(index_of[owner], i, True))      # every run has a cache entry of its own
     return ModelSpec(architecture=ARCHITECTURE, hidden_size=width, vocab_size=vocab,
                      max_position_embeddings=MAX_POSITIONS, layers=tuple(layers), run_order=tuple(run_order),
                      final_norm=norm, tie_word_embeddings=True, eos_token_ids=(),

@@ -31,7 +31,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
                                const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_q,
                                const int* __restrict__ kv_lens, const float* __restrict__ sinks, int nq, int nkv,
                                int dk, int dv, int page_size, float scale, int window, int nsplit, int kv_chunk,
-                               float* __restrict__ part_o, float* __restrict__ part_ml, ScoreMods mods) {
+                               float* __restrict__ part_o, float* __restrict__ part_ml, ScoreMods mods, HeadGate gate) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   extern __shared__ float smem[];
@@ -180,7 +180,7 @@ paged_attention_general_kernel(const float* __restrict__ q, const TC* __restrict
       }
       continue;
     }
-    const float inv = 1.f / l[i];
+    const float inv = head_gate_of(gate, (size_t)(t0 + row / G), kvh * G + row % G) / l[i];
     TO* o = out + ((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dv;
 #pragma unroll
     for (int c = 0; c < VPL; ++c) {
@@ -197,7 +197,7 @@ constexpr int kMaxSlices = 64;
 template <typename TO>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        TO* __restrict__ out, const int* __restrict__ cu_q, int n_entries, int nq,
-                                       int nkv, int dv, int nsplit, int rows_padded) {
+                                       int nkv, int dv, int nsplit, int rows_padded, HeadGate gate) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   __shared__ float w[kMaxSlices];
@@ -220,7 +220,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
       L += part_ml[(first + (size_t)s * rows_padded) * 2 + 1] * ws;
     }
     L = warp_sum(L);
-    if (lane == 0) inv_l = 1.f / L;
+    if (lane == 0) inv_l = head_gate_of(gate, (size_t)(t0 + r / G), kvh * G + r % G) / L;
   }
   __syncthreads();
   TO* o = out + ((size_t)(t0 + r / G) * nq + kvh * G + r % G) * dv;
@@ -325,14 +325,14 @@ static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, 
                           const void* v_cache, void* out, const int* block_table, int table_stride, const int* cu_q,
                           const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
                           float scale, int window, int nsplit, int kv_chunk, float* part_o, float* part_ml,
-                          int n_entries, ScoreMods mods) {
+                          int n_entries, ScoreMods mods, HeadGate gate) {
 #define SRLM_GENERAL_CASE(V)                                                                                   \
   case V: {                                                                                                    \
     auto kern = paged_attention_general_kernel<TC, TO, V>;                                                     \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     launch_pdl(kern, dim3(grid), dim3(kWarps * 32), smem, stream, q, (const TC*)k_cache, (const TC*)v_cache, (TO*)out, block_table, \
                                               table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size,  \
-                                              scale, window, nsplit, kv_chunk, part_o, part_ml, mods);         \
+                                              scale, window, nsplit, kv_chunk, part_o, part_ml, mods, gate);   \
     break;                                                                                                     \
   }
   switch (vpl) {
@@ -346,7 +346,7 @@ static int launch_general(int vpl, dim3 grid, size_t smem, cudaStream_t stream, 
   if (nsplit > 1) {
     const long long blocks = (long long)n_entries * nkv * kRows;
     launch_pdl(attention_merge_kernel<TO>, dim3((unsigned)blocks), dim3(128), 0, stream, part_o, part_ml, (TO*)out, cu_q, n_entries, nq,
-                                                                     nkv, dv, nsplit, kRows);
+                                                                     nkv, dv, nsplit, kRows, gate);
   }
   return launched();
 }
@@ -363,8 +363,10 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
                                             const float* sinks, int n_entries, int max_q_len, int nq, int nkv,
                                             int dk, int dv, int page_size, float scale, int window, int nsplit,
                                             int kv_chunk, float* part_o, float* part_ml, const float* head_scale,
-                                            const float* pen_weight, const float* pen_rate, cudaStream_t stream) {
+                                            const float* pen_weight, const float* pen_rate, const float* gate_logits,
+                                            long long ld_gate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  const HeadGate gate{gate_logits, ld_gate};
   if ((pen_weight == nullptr) != (pen_rate == nullptr))
     return refuse(ST_BAD_SIZE, "paged_attention_general: a distance penalty needs its weight and its rate");
   const ScoreMods mods{head_scale, pen_weight, pen_rate};
@@ -388,15 +390,15 @@ extern "C" int srlm_paged_attention_general(const float* q, const void* k_cache,
   if (cache_dtype == DT_F32 && out_dtype == DT_F32)
     return launch_general<float, float>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
                                         cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
-                                        part_o, part_ml, n_entries, mods);
+                                        part_o, part_ml, n_entries, mods, gate);
   if (cache_dtype == DT_BF16 && out_dtype == DT_F32)
     return launch_general<bf16, float>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
                                        cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
-                                        part_o, part_ml, n_entries, mods);
+                                        part_o, part_ml, n_entries, mods, gate);
   if (cache_dtype == DT_BF16 && out_dtype == DT_BF16)
     return launch_general<bf16, bf16>(vpl, grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride,
                                       cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale, window, nsplit, kv_chunk,
-                                        part_o, part_ml, n_entries, mods);
+                                        part_o, part_ml, n_entries, mods, gate);
   return refuse(ST_BAD_DTYPE, "paged_attention_general: cache dtype %d with output dtype %d", cache_dtype, out_dtype);
 }
 
@@ -427,17 +429,19 @@ extern "C" int srlm_attention_bias_append(const void* proj, int proj_dtype, long
 // Adds the slices that a sliced attention kernel left in part_o [.., rows_padded, dv] / part_ml [.., rows_padded, 2].
 extern "C" int srlm_attention_general_merge(const float* part_o, const float* part_ml, void* out, int out_dtype,
                                             const int* cu_q, int n_entries, int nq, int nkv, int dv, int nsplit,
-                                            int rows_padded, cudaStream_t stream) {
+                                            int rows_padded, const float* gate_logits, long long ld_gate,
+                                            cudaStream_t stream) {
   if (n_entries <= 0 || nsplit <= 1) return ST_OK;
+  const HeadGate gate{gate_logits, ld_gate};
   if (nsplit > kMaxSlices || rows_padded <= 0)
     return refuse(ST_BAD_SIZE, "attention_general_merge: %d slices (at most %d), %d rows", nsplit, kMaxSlices, rows_padded);
   const long long blocks = (long long)n_entries * nkv * rows_padded;
   if (out_dtype == DT_F32)
     launch_pdl(attention_merge_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, stream, part_o, part_ml, (float*)out, cu_q, n_entries, nq,
-                                                                        nkv, dv, nsplit, rows_padded);
+                                                                        nkv, dv, nsplit, rows_padded, gate);
   else if (out_dtype == DT_BF16)
     launch_pdl(attention_merge_kernel<bf16>, dim3((unsigned)blocks), dim3(128), 0, stream, part_o, part_ml, (bf16*)out, cu_q, n_entries, nq,
-                                                                       nkv, dv, nsplit, rows_padded);
+                                                                       nkv, dv, nsplit, rows_padded, gate);
   else
     return refuse(ST_BAD_DTYPE, "attention_general_merge: output dtype %d", out_dtype);
   return launched();

@@ -53,7 +53,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
                                    const float* __restrict__ sinks, int nq, int nkv, int dk, int dv, int page_size,
                                    float scale, int window, int nbuf, const bf16* __restrict__ kv_rows,
                                    long long ld_rows, const int* __restrict__ cu_kv, int dim_rows, int v_off,
-                                   int page_skip, ScoreMods mods) {
+                                   int page_skip, ScoreMods mods, HeadGate gate) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   // kv_rows != null: every query head has keys and values of its own (nkv = nq), formed for this step in
@@ -264,7 +264,7 @@ paged_attention_general_mma_kernel(const float* __restrict__ q, const bf16* __re
   for (int i = 0; i < 2; ++i) {
     const int row = r0 + warp * 16 + (lane >> 2) + 8 * i;
     if (row >= rows) continue;
-    const float inv = 1.f / l[i];
+    const float inv = head_gate_of(gate, (size_t)(t0 + row / G), kvh * G + row % G) / l[i];
     TO* dst = out + ((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dv + slab * DVT + (lane & 3) * 2;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
@@ -293,7 +293,7 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
                                       const float* __restrict__ sinks, int nq, int nkv, int dk, int dv,
                                       int page_size, float scale, int window, int nsplit, int kv_chunk,
                                       float* __restrict__ part_o, float* __restrict__ part_ml, int row_tiles,
-                                      ScoreMods mods) {
+                                      ScoreMods mods, HeadGate gate) {
   pdl_wait();        // launched as a dependent of the kernel ahead: nothing is read before it has finished
   pdl_trigger();
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -478,7 +478,7 @@ paged_attention_general_decode_kernel(const float* __restrict__ q, const bf16* _
         part_ml[slab * 2 + 1] = l[i];
       }
     } else {
-      const float inv = 1.f / l[i];
+      const float inv = head_gate_of(gate, (size_t)(t0 + row / G), kvh * G + row % G) / l[i];
       TO* dst = out + ((size_t)(t0 + row / G) * nq + kvh * G + row % G) * dv + col0;
 #pragma unroll
       for (int n = 0; n < NTW; ++n) {
@@ -495,12 +495,12 @@ static int launch_mma(dim3 grid, size_t smem, cudaStream_t stream, const float* 
                       const int* kv_lens, const float* sinks, int nq, int nkv, int dk, int dv, int page_size,
                       float scale, int window, int nbuf, const bf16* kv_rows = nullptr, long long ld_rows = 0,
                       const int* cu_kv = nullptr, int dim_rows = 0, int v_off = 0, int page_skip = 0,
-                      ScoreMods mods = ScoreMods{nullptr, nullptr, nullptr}) {
+                      ScoreMods mods = ScoreMods{nullptr, nullptr, nullptr}, HeadGate gate = HeadGate{nullptr, 0}) {
   auto kern = paged_attention_general_mma_kernel<TO, NT>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   launch_pdl(kern, dim3(grid), dim3(kMmaWarps * 32), smem, stream, q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out, block_table,
                                                table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, page_size, scale,
-                                               window, nbuf, kv_rows, ld_rows, cu_kv, dim_rows, v_off, page_skip, mods);
+                                               window, nbuf, kv_rows, ld_rows, cu_kv, dim_rows, v_off, page_skip, mods, gate);
   return launched();
 }
 
@@ -523,8 +523,10 @@ extern "C" int srlm_paged_attention_general_mma(const float* q, const void* k_ca
                                                 const int* cu_q, const int* kv_lens, const float* sinks,
                                                 int n_entries, int max_q_len, int nq, int nkv, int dk, int dv,
                                                 int page_size, float scale, int window, const float* head_scale,
-                                                const float* pen_weight, const float* pen_rate, cudaStream_t stream) {
+                                                const float* pen_weight, const float* pen_rate,
+                                                const float* gate_logits, long long ld_gate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  const HeadGate gate{gate_logits, ld_gate};
   if ((pen_weight == nullptr) != (pen_rate == nullptr))
     return refuse(ST_BAD_SIZE, "paged_attention_general_mma: a distance penalty needs its weight and its rate");
   const ScoreMods mods{head_scale, pen_weight, pen_rate};
@@ -545,7 +547,7 @@ extern "C" int srlm_paged_attention_general_mma(const float* q, const void* k_ca
   const int nbuf = q_bytes + 2 * tile_bytes <= 100 * 1024 ? 2 : 1;
   const size_t smem = q_bytes + nbuf * tile_bytes;
 #define SRLM_MMA_ARGS grid, smem, stream, q, k_cache, v_cache, out, block_table, table_stride, cu_q, kv_lens, sinks, nq, \
-                      nkv, dk, dv, page_size, scale, window, nbuf, nullptr, 0, nullptr, 0, 0, 0, mods
+                      nkv, dk, dv, page_size, scale, window, nbuf, nullptr, 0, nullptr, 0, 0, 0, mods, gate
   if (out_dtype == DT_F32) return slab == 128 ? launch_mma<float, 16>(SRLM_MMA_ARGS) : launch_mma<float, 8>(SRLM_MMA_ARGS);
   if (out_dtype == DT_BF16) return slab == 128 ? launch_mma<bf16, 16>(SRLM_MMA_ARGS) : launch_mma<bf16, 8>(SRLM_MMA_ARGS);
 #undef SRLM_MMA_ARGS
@@ -566,8 +568,10 @@ extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k
                                                    int n_entries, int max_q_len, int nq, int nkv, int dk, int dv,
                                                    int page_size, float scale, int window, int nsplit, int kv_chunk,
                                                    float* part_o, float* part_ml, const float* head_scale,
-                                                   const float* pen_weight, const float* pen_rate, cudaStream_t stream) {
+                                                   const float* pen_weight, const float* pen_rate,
+                                                   const float* gate_logits, long long ld_gate, cudaStream_t stream) {
   if (n_entries <= 0 || max_q_len <= 0) return ST_OK;
+  const HeadGate gate{gate_logits, ld_gate};
   if ((pen_weight == nullptr) != (pen_rate == nullptr))
     return refuse(ST_BAD_SIZE, "paged_attention_general_decode: a distance penalty needs its weight and its rate");
   const ScoreMods mods{head_scale, pen_weight, pen_rate};
@@ -591,7 +595,7 @@ extern "C" int srlm_paged_attention_general_decode(const float* q, const void* k
     launch_pdl(kern, dim3(grid), dim3(kMmaWarps * 32), smem, stream, q, (const bf16*)k_cache, (const bf16*)v_cache, (TO*)out,          \
                                                  block_table, table_stride, cu_q, kv_lens, sinks, nq, nkv, dk, dv, \
                                                  page_size, scale, window, nsplit, kv_chunk, part_o, part_ml,      \
-                                                 row_tiles, mods);                                                 \
+                                                 row_tiles, mods, gate);                                           \
   } while (0)
 #define SRLM_DEC_SIZES(TO)                                \
   do {                                                    \

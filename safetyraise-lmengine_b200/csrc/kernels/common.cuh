@@ -79,6 +79,16 @@ __device__ __forceinline__ float distance_penalty(float weight, float rate, int 
   return weight * log1pf(rate * (float)distance);
 }
 
+// Optional gate on the output of an attention: head h of token t is multiplied by logistic(logits[t * ld + h])
+// (float32 logits, e.g. columns of the mixer's stacked projection); logits null: no gate.
+struct HeadGate {
+  const float* logits;
+  long long ld;
+};
+__device__ __forceinline__ float head_gate_of(const HeadGate& g, size_t token, int head) {
+  return g.logits ? 1.f / (1.f + expf(-g.logits[token * g.ld + head])) : 1.f;
+}
+
 // Sum over a block in a fixed order (depends on blockDim only).  scratch: 32 floats.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;

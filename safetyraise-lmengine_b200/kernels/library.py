@@ -788,14 +788,15 @@ class KernelLibrary:
     GENERAL_ROWS = 16        # rows (tokens x query heads of a KV head) of a block of the general attention kernel
 
     def paged_attention_general(self, ctx, q, k_cache, v_cache, out, block_table, sinks, nq, nkv, dk, dv, scale,
-                                window=0, head_scale=None, penalty=None):
+                                window=0, head_scale=None, penalty=None, gate=None):
         """Causal attention of the batch of ``ctx`` over pages whose keys have dk and whose values have dv
         elements (v_cache None: the values are the keys' first dv elements).  q float32 [T, nq * dk];
         k_cache [pages, nkv, page_size, dk]; out [T, nq * dv], float32 or the cache's dtype; sinks float32
         [nq] or None: one more term exp(sink) in each head's softmax denominator.  head_scale float32 [nq] or
         None: a factor per head on the scaled scores.  penalty (weight, rate), float32 [nq] each, or None:
         weight * ln(1 + rate * distance to the key) is taken off the score.  window > 0: a query sees itself
-        and the window - 1 keys before it.
+        and the window - 1 keys before it.  gate (float32 tensor [T, >= column + nq], column) or None: head h of
+        token t is multiplied by the logistic of tensor[t, column + h] as it is written.
 
         A bfloat16 cache: the tensor-core forms (attention_general_mma.cu) when they take the sizes -- the
         decode form for steps of at most four tokens an entry (keys in slices, as many blocks as run at the
@@ -807,6 +808,13 @@ class KernelLibrary:
         n = ctx.n_entries
         g = nq // nkv
         mods = (_ptr(head_scale), _ptr(penalty[0] if penalty else None), _ptr(penalty[1] if penalty else None))
+        if gate is not None:
+            logits, column = gate
+            if logits.dtype != torch.float32 or not logits.is_cuda or logits.stride(1) != 1 or logits.shape[1] < column + nq:
+                raise ShapeError("paged_attention_general: the gate's logits are float32 columns of a row-major tensor")
+            gate_args = (C.c_void_p(logits.data_ptr() + 4 * column), C.c_longlong(logits.stride(0)))
+        else:
+            gate_args = (C.c_void_p(0), C.c_longlong(0))
         bf16 = k_cache.dtype == torch.bfloat16
         tensor_cores = bf16 and self.general_attention_on_tensor_cores
         from_keys = C.c_int(int(v_cache is None))
@@ -830,11 +838,11 @@ class KernelLibrary:
                 C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks), C.c_int(n),
                 C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv), C.c_int(k_cache.shape[2]),
                 C.c_float(scale), C.c_int(window or 0), C.c_int(nsplit), C.c_int(chunk), _ptr(part_o), _ptr(part_ml),
-                *mods, _stream()), "paged_attention_general_decode")
+                *mods, *gate_args, _stream()), "paged_attention_general_decode")
             if nsplit > 1:
                 self._check(self.lib.srlm_attention_general_merge(
                     _ptr(part_o), _ptr(part_ml), _ptr(out), dtype_code(out.dtype), _ptr(ctx.cu_q), C.c_int(n),
-                    C.c_int(nq), C.c_int(nkv), C.c_int(dv), C.c_int(nsplit), C.c_int(rows_padded), _stream()),
+                    C.c_int(nq), C.c_int(nkv), C.c_int(dv), C.c_int(nsplit), C.c_int(rows_padded), *gate_args, _stream()),
                     "attention_general_merge")
             return
         decode = ctx.max_q_len * g <= self.GENERAL_ROWS
@@ -845,7 +853,7 @@ class KernelLibrary:
                 _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), dtype_code(out.dtype), _ptr(block_table),
                 C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks), C.c_int(n),
                 C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
-                C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), *mods, _stream()),
+                C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), *mods, *gate_args, _stream()),
                 "paged_attention_general_mma")
             return
         # float32, and sizes the tensor-core forms do not take: float32 arithmetic; a bfloat16 decode step in slices
@@ -863,7 +871,7 @@ class KernelLibrary:
             _ptr(block_table), C.c_int(block_table.stride(0)), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), _ptr(sinks),
             C.c_int(n), C.c_int(ctx.max_q_len), C.c_int(nq), C.c_int(nkv), C.c_int(dk), C.c_int(dv),
             C.c_int(k_cache.shape[2]), C.c_float(scale), C.c_int(window or 0), C.c_int(nsplit), C.c_int(chunk),
-            _ptr(part_o), _ptr(part_ml), *mods, _stream()), "paged_attention_general")
+            _ptr(part_o), _ptr(part_ml), *mods, *gate_args, _stream()), "paged_attention_general")
         if nsplit > 1:
             self.launches += 1           # the kernel that adds the slices
 

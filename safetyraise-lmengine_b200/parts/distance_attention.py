@@ -96,10 +96,9 @@ class DistanceAttention(Part):
             if gated:
                 ops.head_gate(attended, proj, self.gate_offset, attended, s.heads, s.v_head_dim)
             return attended
-        raw = ctx.workspace.get("dist_attn.raw", T, s.heads * s.v_head_dim, torch.float32) if gated else attended
-        ops.paged_attention_general(ctx, q, k_pool, v_pool, raw, ctx.block_tables[group], None, s.heads, s.kv_heads,
+        # the gate is applied where the general kernels write a head's output (the kernel that adds key slices included)
+        ops.paged_attention_general(ctx, q, k_pool, v_pool, attended, ctx.block_tables[group], None, s.heads, s.kv_heads,
                                     s.head_dim, s.v_head_dim, s.softmax_scale, s.window or 0,
-                                    head_scale=self.temperature, penalty=self.penalty)
-        if gated:
-            ops.head_gate(raw, proj, self.gate_offset, attended, s.heads, s.v_head_dim)
+                                    head_scale=self.temperature, penalty=self.penalty,
+                                    gate=(proj, self.gate_offset) if gated else None)
         return attended

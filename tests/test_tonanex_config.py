@@ -78,6 +78,8 @@ def test_a_model_without_cap_window_or_shared_expert():
     (lambda c: c["layers"][0]["mixer"]["mask"].update(size=0), ConfigError),
     (lambda c: c["layers"][1]["mlp"]["router"].update(top=6), ConfigError),
     (lambda c: c["layers"][2].update(weights_of=2), ConfigError),
+    (lambda c: c["layers"][2].update(weights_of=9), ConfigError),
+    (lambda c: (c["layers"][1].update(weights_of=2), c["layers"][2].update(weights_of=1)), ConfigError),   # a ring
     (lambda c: c["layers"][2].update(weights_of=0), ConfigError),       # differs from the layer it borrows from
     (lambda c: c.pop("norm"), ConfigError),
     (lambda c: c.update(logit_softcap=-1.0), ConfigError),
@@ -95,3 +97,12 @@ def test_a_chain_of_borrowers_ends_at_the_owner():
     cfg["layers"].append(dict(copy.deepcopy(cfg["layers"][2]), weights_of=2))
     spec = spec_from_config(cfg)
     assert spec.run_order[-1].layer == 1 and spec.run_order[-1].cache == 5
+
+
+def test_a_layer_may_borrow_from_a_later_one():
+    cfg = copy.deepcopy(CFG)
+    cfg["layers"][0]["weights_of"] = 4
+    del cfg["layers"][4]["weights_of"]
+    spec = spec_from_config(cfg)
+    assert [l.weight_prefix for l in spec.layers] == ["l1.", "l3.", "l4."]
+    assert [(s.layer, s.cache) for s in spec.run_order] == [(2, 0), (0, 1), (0, 2), (1, 3), (2, 4)]

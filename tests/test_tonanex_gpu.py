@@ -478,6 +478,15 @@ def test_attention_kernel_window_edges_penalty_and_temperature(cache_dtype, dk, 
                                     head_scale=temperature.to(dev), penalty=(weight.to(dev), rate.to(dev)))
         err = (out.cpu().double().view(n, heads, dv) - ref[L - n:]).abs().max() / ref.abs().max()
         assert err < tol, (q_lens, float(err))
+        # the same with a gate per head on the way out: columns 3.. of a wider tensor of logits
+        logits = 2 * torch.randn(n, heads + 5, generator=g)
+        ops.paged_attention_general(_Ctx(q_lens, [L], dev), q[L - n:].reshape(n, -1).contiguous().to(dev), k_pool, v_pool,
+                                    out, table, None, heads, kv_heads, dk, dv, scale, window,
+                                    head_scale=temperature.to(dev), penalty=(weight.to(dev), rate.to(dev)),
+                                    gate=(logits.to(dev), 3))
+        gated = ref[L - n:] * torch.sigmoid(logits[:, 3:3 + heads].double())[:, :, None]
+        err = (out.cpu().double().view(n, heads, dv) - gated).abs().max() / ref.abs().max()
+        assert err < tol, ("gated", q_lens, float(err))
         ctx = _Ctx(q_lens, [L], dev)
         if cache_dtype == torch.bfloat16 and dk == dv and n > 4 and ops.sinks_on_tcgen05(ctx, cache_dtype, heads, kv_heads, dk, dv, page):
             # heads of 128: the tensor-memory kernel, queries in bfloat16
