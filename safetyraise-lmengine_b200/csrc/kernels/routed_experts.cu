@@ -30,17 +30,13 @@ __device__ __forceinline__ float clamped_glu(float gate, float up, float limit, 
   return g * (1.f / (1.f + expf(-alpha * g))) * (u + 1.f);
 }
 
-// One warp per token.  The row of logits sits in shared memory; `top` times the warp takes the largest
-// value left (ties: the lowest index) and strikes it out.  weights = softmax over the chosen values.
-__global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ bias,
-                                 int T, int E, int top, int* __restrict__ choice, float* __restrict__ weight) {
-  pdl_wait();
-  pdl_trigger();
-  extern __shared__ float route_smem[];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  const int t = blockIdx.x * warps + warp;
-  if (t >= T) return;
-  float* z = route_smem + (size_t)warp * E;
+// One warp routes a token.  The row of logits sits in shared memory (z: E floats of the warp's own); `top` times
+// the warp takes the largest value left (ties: the lowest index) and strikes it out.  weights = softmax over the
+// chosen values.
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, long long ld, const float* __restrict__ bias,
+                                            int t, int E, int top, float* z, int* __restrict__ choice,
+                                            float* __restrict__ weight) {
+  const int lane = threadIdx.x & 31;
   for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)t * ld + e] + (bias ? bias[e] : 0.f);
   __syncwarp();
   float first = 0.f, sum = 0.f;
@@ -70,6 +66,18 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
   }
   __syncwarp();
   for (int c = lane; c < top; c += 32) weight[(size_t)t * top + c] /= sum;
+  __syncwarp();
+}
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ bias,
+                                 int T, int E, int top, int* __restrict__ choice, float* __restrict__ weight) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ float route_smem[];
+  const int warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int t = blockIdx.x * warps + warp;
+  if (t >= T) return;
+  route_token(logits, ld, bias, t, E, top, route_smem + (size_t)warp * E, choice, weight);
 }
 
 // One block.  offsets[E + 1]: first row of each expert; tiles[E + 1]: first tile of each expert (tiles of
@@ -78,14 +86,23 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, long long ld,
 // align: every expert's rows start at a multiple of tile_rows (for products whose tiles are fixed rows of their
 // operands); pair_of_row then has rows_cap entries, -1 where a row holds no pair, and group_of_tile[max_tiles]
 // names the expert of every tile, -1 for a tile without rows.
-__global__ void moe_sort_kernel(const int* __restrict__ choice, int n, int E, int tile_rows, int align,
+// logits != null: the block first routes the n / top tokens itself (small steps: one launch fewer), a warp a
+// token at a time, and writes choice and weight; then it orders what it chose.
+__global__ void moe_sort_kernel(int* __restrict__ choice, int n, int E, int tile_rows, int align,
                                 int* __restrict__ offsets, int* __restrict__ tiles, int* __restrict__ pair_of_row,
-                                int* __restrict__ row_of_pair, int* __restrict__ group_of_tile, int max_tiles, int rows_cap) {
+                                int* __restrict__ row_of_pair, int* __restrict__ group_of_tile, int max_tiles, int rows_cap,
+                                const float* __restrict__ logits, long long ld, const float* __restrict__ bias, int top,
+                                float* __restrict__ weight) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ int sort_smem[];
   int* count = sort_smem;            // [E]
   int* start = count + E;            // [E + 1]
+  if (logits) {
+    float* z = reinterpret_cast<float*>(start + E + 1) + (size_t)(threadIdx.x >> 5) * E;
+    for (int t = threadIdx.x >> 5; t < n / top; t += blockDim.x >> 5) route_token(logits, ld, bias, t, E, top, z, choice, weight);
+    __syncthreads();                 // the choices of all tokens are written (and visible to the block)
+  }
   for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
   if (align) {
     for (int i = threadIdx.x; i < rows_cap; i += blockDim.x) pair_of_row[i] = -1;
@@ -380,15 +397,15 @@ __global__ void moe_combine_kernel(const TR* __restrict__ rows, long long ldr, c
   }
 }
 
-// in [T, 2 F]: gate in columns [0, F), up in [F, 2 F)  ->  out [T, F]
+// in [T, ld >= 2 F]: gate in columns [0, F), up in [F, 2 F)  ->  out [T, F]
 template <typename TI, typename TA>
-__global__ void clamped_glu_kernel(const TI* __restrict__ in, TA* __restrict__ out, int F, size_t total, float limit,
-                                   float alpha) {
+__global__ void clamped_glu_kernel(const TI* __restrict__ in, long long ld, TA* __restrict__ out, int F, size_t total,
+                                   float limit, float alpha) {
   pdl_wait();
   pdl_trigger();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / F, f = idx - t * F;
-    out[idx] = from_float<TA>(clamped_glu(to_float(in[t * 2 * F + f]), to_float(in[t * 2 * F + F + f]), limit, alpha));
+    out[idx] = from_float<TA>(clamped_glu(to_float(in[t * ld + f]), to_float(in[t * ld + F + f]), limit, alpha));
   }
 }
 
@@ -415,18 +432,27 @@ extern "C" int srlm_moe_route(const float* logits, long long ld, const float* bi
 // tile_rows 0: the tiles of the grouped kernels of this file, rows packed.  tile_rows > 0: every expert's rows
 // start at a multiple of it; group_of_tile [max_tiles >= (n + E * (tile_rows - 1)) / tile_rows] names each tile's
 // expert (-1: none) and pair_of_row has rows_cap >= max_tiles * tile_rows entries (-1: no pair).
-extern "C" int srlm_moe_sort(const int* choice, int n, int E, int* offsets, int* tiles, int* pair_of_row,
+// logits (float32 [n / top, ld >= E], with bias [E] or null) given: the kernel routes the tokens first and
+// writes choice and weight [n / top, top] itself; offered for E <= 256 (srlm_moe_sort_routes).
+extern "C" int srlm_moe_sort_routes(int tokens, int E) { return tokens <= 512 && E <= 256; }
+
+extern "C" int srlm_moe_sort(int* choice, int n, int E, int* offsets, int* tiles, int* pair_of_row,
                              int* row_of_pair, int tile_rows, int* group_of_tile, int max_tiles, int rows_cap,
+                             const float* logits, long long ld, const float* bias, int top, float* weight,
                              cudaStream_t stream) {
   if (n <= 0) return ST_OK;
   if (E <= 0 || E > 4096) return refuse(ST_BAD_SIZE, "moe_sort: experts=%d (at most 4096)", E);
+  if (logits && (top <= 0 || top > E || n % top || ld < E || !weight || !srlm_moe_sort_routes(n / top, E)))
+    return refuse(ST_BAD_SIZE, "moe_sort: routing %d pairs, top=%d of %d experts, ld=%lld", n, top, E, ld);
   const int align = tile_rows > 0;
   if (align && (!group_of_tile || (long long)max_tiles < ((long long)n + (long long)E * (tile_rows - 1)) / tile_rows ||
                 rows_cap < max_tiles * tile_rows))
     return refuse(ST_BAD_SIZE, "moe_sort: %d pairs over %d experts in tiles of %d need more than %d tiles, %d rows", n, E,
                   tile_rows, max_tiles, rows_cap);
-  launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * E + 1) * sizeof(int), stream, choice, n, E,
-             align ? tile_rows : kTile, align, offsets, tiles, pair_of_row, row_of_pair, group_of_tile, max_tiles, rows_cap);
+  const size_t smem = (size_t)(2 * E + 1) * sizeof(int) + (logits ? (size_t)32 * E * sizeof(float) : 0);
+  launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), smem, stream, choice, n, E,
+             align ? tile_rows : kTile, align, offsets, tiles, pair_of_row, row_of_pair, group_of_tile, max_tiles, rows_cap,
+             logits, ld, bias, top, weight);
   return launched();
 }
 
@@ -498,15 +524,15 @@ extern "C" int srlm_moe_combine(const void* rows, int rows_dtype, long long ldr,
   return launched();
 }
 
-// in [T, 2 F] (float32 or the activation dtype): gate columns, then up columns; out [T, F]
-extern "C" int srlm_clamped_glu(const void* in, int in_dtype, void* out, int out_dtype, int T, int F, float limit,
-                                float alpha, cudaStream_t stream) {
+// in [T, ld >= 2 F] (float32 or the activation dtype): gate columns, then up columns; out [T, F]
+extern "C" int srlm_clamped_glu(const void* in, int in_dtype, long long ld, void* out, int out_dtype, int T, int F,
+                                float limit, float alpha, cudaStream_t stream) {
   if (T <= 0) return ST_OK;
-  if (F <= 0) return refuse(ST_BAD_SIZE, "clamped_glu: F=%d", F);
+  if (F <= 0 || ld < 2ll * F) return refuse(ST_BAD_SIZE, "clamped_glu: F=%d ld=%lld", F, ld);
   const size_t total = (size_t)T * F;
   size_t g = (total + 255) / 256;
   const int grid = (int)(g > 148 * 16 ? 148 * 16 : g);
-#define SRLM_GLU(TI, TA) launch_pdl(clamped_glu_kernel<TI, TA>, dim3(grid), dim3(256), 0, stream, (const TI*)in, (TA*)out, F, total, limit, alpha)
+#define SRLM_GLU(TI, TA) launch_pdl(clamped_glu_kernel<TI, TA>, dim3(grid), dim3(256), 0, stream, (const TI*)in, ld, (TA*)out, F, total, limit, alpha)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) SRLM_GLU(float, float);
   else if (in_dtype == DT_F32 && out_dtype == DT_BF16) SRLM_GLU(float, bf16);
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) SRLM_GLU(bf16, bf16);

@@ -907,25 +907,47 @@ class KernelLibrary:
     def moe_tile_rows(self) -> int:
         return int(self.lib.srlm_moe_tile_rows())
 
-    def moe_route(self, logits, bias, top, choice, weight):
+    @staticmethod
+    def _columns(t, column, width):
+        """(pointer, leading dimension) of the float32 columns [column, column + width) of a row-major tensor."""
+        if t.dtype != torch.float32 or not t.is_cuda or t.stride(1) != 1 or t.shape[1] < column + width:
+            raise ShapeError("float32 columns of a row-major CUDA tensor are wanted")
+        return C.c_void_p(t.data_ptr() + 4 * column), C.c_longlong(t.stride(0))
+
+    def moe_route(self, logits, bias, top, choice, weight, column=0, experts=None):
         """logits float32 [T, E] (+ bias float32 [E]) -> choice int32 [T, top], the experts with the largest
-        logits (ties: the lowest index), and weight float32 [T, top], the softmax over the chosen logits."""
-        T, E = logits.shape
-        if logits.dtype != torch.float32 or choice.dtype != torch.int32 or weight.dtype != torch.float32:
+        logits (ties: the lowest index), and weight float32 [T, top], the softmax over the chosen logits.
+        column / experts: the logits are those columns of a wider tensor."""
+        T = logits.shape[0]
+        E = logits.shape[1] - column if experts is None else experts
+        if choice.dtype != torch.int32 or weight.dtype != torch.float32:
             raise ShapeError("moe_route: float32 logits and weights, int32 choices")
-        self._check(self.lib.srlm_moe_route(_ptr(logits), C.c_longlong(logits.stride(0)), _ptr(bias), C.c_int(T), C.c_int(E),
+        ptr, ld = self._columns(logits, column, E)
+        self._check(self.lib.srlm_moe_route(ptr, ld, _ptr(bias), C.c_int(T), C.c_int(E),
                                             C.c_int(top), _ptr(choice), _ptr(weight), _stream()), "moe_route")
 
-    def moe_sort(self, choice, experts, offsets, tiles, pair_of_row, row_of_pair, tile_rows=0, group_of_tile=None):
+    def moe_sort_routes(self, tokens, experts) -> bool:
+        """Whether moe_sort(..., route=...) routes a step of this many tokens itself."""
+        return bool(self.lib.srlm_moe_sort_routes(C.c_int(tokens), C.c_int(experts)))
+
+    def moe_sort(self, choice, experts, offsets, tiles, pair_of_row, row_of_pair, tile_rows=0, group_of_tile=None,
+                 route=None):
         """The (token, choice) pairs ordered by expert: offsets / tiles int32 [experts + 1] (first row and first
         tile of each expert), pair_of_row / row_of_pair int32 [pairs].  tile_rows > 0: every expert's rows start at
         a multiple of tile_rows; pair_of_row then covers all rows of group_of_tile's tiles (-1: a row without a
-        pair) and group_of_tile int32 [tiles] names each tile's expert (-1: none)."""
+        pair) and group_of_tile int32 [tiles] names each tile's expert (-1: none).  route (logits, column, bias,
+        weight): the kernel first routes the tokens itself, as moe_route does, and writes choice and weight."""
+        if route is not None:
+            logits, column, bias, weight = route
+            ptr, ld = self._columns(logits, column, experts)
+            routing = (ptr, ld, _ptr(bias), C.c_int(choice.shape[1]), _ptr(weight))
+        else:
+            routing = (C.c_void_p(0), C.c_longlong(0), C.c_void_p(0), C.c_int(0), C.c_void_p(0))
         self._check(self.lib.srlm_moe_sort(
             _ptr(choice), C.c_int(choice.numel()), C.c_int(experts), _ptr(offsets), _ptr(tiles), _ptr(pair_of_row),
             _ptr(row_of_pair), C.c_int(tile_rows), _ptr(group_of_tile),
             C.c_int(group_of_tile.numel() if group_of_tile is not None else 0),
-            C.c_int(pair_of_row.numel()), _stream()), "moe_sort")
+            C.c_int(pair_of_row.numel()), *routing, _stream()), "moe_sort")
 
     GROUPED_TILE = 128       # token rows of a tile of the grouped tensor-memory product
 
@@ -981,10 +1003,11 @@ class KernelLibrary:
             _ptr(out), dtype_code(out.dtype), C.c_int(T), C.c_int(weight.shape[1]), C.c_int(H), _stream()), "moe_combine")
 
     def clamped_glu(self, gate_up, out, limit, alpha):
-        """out [T, F] = g * logistic(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate_up [T, 2 F]:
-        gate columns, then up columns."""
+        """out [T, F] = g * logistic(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit); gate_up
+        [T, >= 2 F]: gate columns, then up columns (whatever follows them is not read)."""
         T, F = out.shape
-        self._check(self.lib.srlm_clamped_glu(_ptr(gate_up), dtype_code(gate_up.dtype), _ptr(out), dtype_code(out.dtype),
+        self._check(self.lib.srlm_clamped_glu(_ptr(gate_up), dtype_code(gate_up.dtype), C.c_longlong(gate_up.stride(0)),
+                                              _ptr(out), dtype_code(out.dtype),
                                               C.c_int(T), C.c_int(F), C.c_float(limit), C.c_float(alpha), _stream()),
                     "clamped_glu")
 

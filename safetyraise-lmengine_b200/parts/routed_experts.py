@@ -30,7 +30,6 @@ class RoutedExperts(Part):
             raise Unsupported(f"routed experts with activation {spec.activation!r} are not implemented")
         self.spec = spec
         p, nm = prefix, spec.expert_names
-        self.router = Linear(tensors[p + nm.router], p + nm.router)
         self.router_bias = tensors[p + nm.router_bias] if spec.router_bias else None
         each = lambda part: [tensors[p + nm.expert.format(e) + part] for e in range(spec.experts)]
         # [experts, 2 ff, hidden] and [experts, hidden, ff].  For the tensor-core product the gate and up rows are
@@ -45,12 +44,15 @@ class RoutedExperts(Part):
             pair = lambda g, u: torch.cat([g, u], dim=0)
         self.gate_up = torch.stack([pair(g, u) for g, u in zip(each(nm.gate), each(nm.up))]).contiguous()
         self.down = torch.stack(each(nm.down)).contiguous()
-        self.shared_gate_up = self.shared_down = None
+        # one product for everything that reads the layer's input whole: the shared expert's gate rows, its up
+        # rows, then the router's rows; its result is float32 (the router's logits are)
+        first, self.shared_down = [tensors[p + nm.router]], None
         if spec.shared_size:
             sp = p + nm.shared
-            self.shared_gate_up = Linear(torch.cat([tensors[sp + nm.gate], tensors[sp + nm.up]], dim=0).contiguous(),
-                                         sp + "gate_up")
+            first = [tensors[sp + nm.gate], tensors[sp + nm.up]] + first
             self.shared_down = Linear(tensors[sp + nm.down], sp + nm.down)
+        self.first = Linear(torch.cat(first, dim=0).contiguous(), p + "shared_gate_up_router")
+        self.router_column = 2 * spec.shared_size
 
     @classmethod
     def tensor_decls(cls, s: RoutedExpertsSpec, prefix: str) -> List[TensorDecl]:
@@ -77,40 +79,44 @@ class RoutedExperts(Part):
         ws = ctx.workspace
         pairs = T * s.top
         # the router in float32: its input may be the activation dtype's rounding of the normed stream
-        logits = self.router(ctx, x, "moe.logits", out_dtype=torch.float32)
+        first = self.first(ctx, x, "moe.first", out_dtype=torch.float32)
         choice = ws.get("moe.choice", T, s.top, torch.int32)
         weight = ws.get("moe.weight", T, s.top, torch.float32)
-        ops.moe_route(logits, self.router_bias, s.top, choice, weight)
         # steps of many tokens (64 rows an expert on average): the experts' products on the persistent tensor-memory
         # kernel, every expert's rows in whole tiles of 128 of a gathered copy of the input
         if (self.interleaved and ops.grouped_products_in_tensor_memory and pairs >= 64 * s.experts
                 and s.intermediate_size % 8 == 0):
-            return self._forward_tiles(ctx, x, choice, weight)
+            ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts)
+            return self._forward_tiles(ctx, x, first, choice, weight)
         heads = ws.get("moe.heads", 2, s.experts + 1, torch.int32, reserve=2)
         order = ws.get("moe.order", 2 * T, s.top, torch.int32, reserve=2 * ws.max_tokens)
         offsets, tiles = heads[0], heads[1]
         pair_of_row, row_of_pair = order[:T].view(-1), order[T:].view(-1)
-        ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair)
+        if ops.moe_sort_routes(T, s.experts):          # a small step: the block that orders the pairs routes them too
+            ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair,
+                         route=(first, self.router_column, self.router_bias, weight))
+        else:
+            ops.moe_route(first, self.router_bias, s.top, choice, weight, column=self.router_column, experts=s.experts)
+            ops.moe_sort(choice, s.experts, offsets, tiles, pair_of_row, row_of_pair)
         y = ws.get("moe.y", pairs, s.intermediate_size, ctx.dtype, reserve=ws.max_tokens * s.top)
         ops.moe_grouped(x, pair_of_row, s.top, self.gate_up, y, offsets, tiles, glu=True, interleaved=self.interleaved,
                         limit=s.limit, alpha=s.glu_alpha)
         rows = ws.get("moe.rows", pairs, H, torch.float32, reserve=ws.max_tokens * s.top)
         ops.moe_grouped(y, None, 1, self.down, rows, offsets, tiles)
         out = ws.get("moe.out", T, H, ctx.dtype)
-        ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, x), out)
+        ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, first), out)
         return out
 
-    def _shared(self, ctx, x):
-        """The output of the expert that every token runs, or None."""
-        if self.shared_gate_up is None:
+    def _shared(self, ctx, first):
+        """The output of the expert that every token runs (its gate and up columns lead the first product), or None."""
+        if self.shared_down is None:
             return None
         s = self.spec
-        gu = self.shared_gate_up(ctx, x, "moe.shared_gu", out_dtype=torch.float32)
-        ys = ctx.workspace.get("moe.shared_y", x.shape[0], s.shared_size, ctx.dtype)
-        ops.clamped_glu(gu, ys, s.shared_limit, s.glu_alpha)
+        ys = ctx.workspace.get("moe.shared_y", first.shape[0], s.shared_size, ctx.dtype)
+        ops.clamped_glu(first, ys, s.shared_limit, s.glu_alpha)
         return self.shared_down(ctx, ys, "moe.shared_out")
 
-    def _forward_tiles(self, ctx, x, choice, weight):
+    def _forward_tiles(self, ctx, x, first, choice, weight):
         s = self.spec
         T, H = x.shape
         ws = ctx.workspace
@@ -130,5 +136,5 @@ class RoutedExperts(Part):
         rows = ws.get("moe.rows_tiles", rows_cap, H, torch.float32, reserve=0)
         ops.gemm_tn_tcgen05_grouped(y, self.down, rows, group_of_tile)
         out = ws.get("moe.out", T, H, ctx.dtype)
-        ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, x), out)
+        ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, first), out)
         return out

@@ -539,6 +539,16 @@ def test_router_choice_and_weights():
             idx[0, :2] = torch.tensor([1, 4])
         assert torch.equal(choice.cpu().long(), idx)
         assert (weight.cpu().double() - torch.softmax(val, -1)).abs().max() < 1e-6
+        # the same from columns of a wider tensor, routed by the block that orders the pairs
+        wide = torch.cat([torch.randn(T, 5, generator=g), z, torch.randn(T, 2, generator=g)], dim=1).to(dev)
+        choice2, weight2 = torch.zeros_like(choice), torch.zeros_like(weight)
+        heads = torch.zeros(2, E + 1, dtype=torch.int32, device=dev)
+        por, rop = torch.zeros(T * top, dtype=torch.int32, device=dev), torch.zeros(T * top, dtype=torch.int32, device=dev)
+        assert ops.moe_sort_routes(T, E)
+        ops.moe_sort(choice2, E, heads[0], heads[1], por, rop, route=(wide, 5, b.to(dev), weight2))
+        assert torch.equal(choice2, choice) and torch.equal(weight2, weight)
+        assert heads[0].tolist() == [int((idx < e).sum()) for e in range(E + 1)]
+        assert all(int(por[int(rop[i])]) == i for i in range(T * top))
 
 
 @pytest.mark.parametrize("dtype,interleaved", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
@@ -649,10 +659,10 @@ def test_cap_and_clamped_activation():
     y = x.to(dev)
     ops.softcap(y, 11.0)
     assert (y.cpu().double() - P.softcap(x.double(), 11.0)).abs().max() < 1e-5
-    gu = 4 * torch.randn(5, 2 * 77, generator=g)
+    gu = 4 * torch.randn(5, 2 * 77 + 9, generator=g)         # columns behind gate and up are not read
     out = torch.zeros(5, 77, device=dev)
     ops.clamped_glu(gu.to(dev), out, 2.5, 1.702)
-    gt, up = gu[:, :77].double().clamp(max=2.5), gu[:, 77:].double().clamp(-2.5, 2.5)
+    gt, up = gu[:, :77].double().clamp(max=2.5), gu[:, 77:154].double().clamp(-2.5, 2.5)
     assert (out.cpu().double() - gt * torch.sigmoid(1.702 * gt) * (up + 1)).abs().max() < 1e-5
 
 
