@@ -36,6 +36,8 @@ scheduler.
 and decode of four-layer Nekedra stacks (each mixer alone, and mixed) beside the
 Qwen3 decoder at equal width, heads and feed-forward size, with the kernels an
 eager step spends its time in (``run_design``).
+``--design tonanex`` does the same for Tonanex stacks with a dense feed-forward
+and with routed experts.
 """
 from __future__ import annotations
 

@@ -1634,15 +1634,18 @@ extern "C" int srlm_gemm_tn_tcgen05_static(const void* X, const void* W, void* C
   return ST_OK;
 }
 
-// Grouped products on the persistent kernel: token tile mt of X (128 rows; X and C hold every group's rows from a
-// multiple of 128 on) multiplies the N weight rows of group group_of_mtile[mt] (device, int32 [ceil(M / 128)];
+// Grouped products on the persistent kernel: token tile mt of X (tile_rows = 128 rows, one SM a tile of 128 weight
+// rows, or 256 rows, a pair of SMs a tile of 256 weight rows; X and C hold every group's rows from a multiple of
+// tile_rows on) multiplies the N weight rows of group group_of_mtile[mt] (device, int32 [ceil(M / tile_rows)];
 // negative: the tile is skipped and its rows of C are not written).  W: [groups * N, K], contiguous.  glu: the
 // weight rows of a group come in blocks of 16 (8 gate rows, then the 8 up rows of the same features) and
 // C [M, N / 2] gets g * logistic(alpha g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
 extern "C" int srlm_gemm_tn_tcgen05_grouped(const void* X, const void* W, void* C, int c_dtype, int M, int N, int K,
-                                            long long ldx, long long ldc, int groups, const int* group_of_mtile, int glu,
-                                            float limit, float alpha, int* err_flag, cudaStream_t stream) {
+                                            long long ldx, long long ldc, int groups, const int* group_of_mtile,
+                                            int tile_rows, int glu, float limit, float alpha, int* err_flag,
+                                            cudaStream_t stream) {
   if (M <= 0) return ST_OK;
+  if (tile_rows != 128 && tile_rows != 256) return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: tiles of %d rows", tile_rows);
   if (N <= 0 || K <= 0 || groups <= 0 || !group_of_mtile || ldx < K || ldc < (glu ? N / 2 : N) || (glu && (N % 16 || !(limit > 0.f))))
     return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: M=%d N=%d K=%d groups=%d ldx=%lld ldc=%lld glu=%d", M, N, K, groups, ldx,
                   ldc, glu);
@@ -1655,7 +1658,9 @@ extern "C" int srlm_gemm_tn_tcgen05_grouped(const void* X, const void* W, void* 
   a.glu_alpha = alpha;
   CUtensorMap mw_copy, mx_copy;
   const CUtensorMap *mw = &mw_copy, *mx = &mx_copy;
+  // (the pair form fetches the tokens of a tile in two boxes of 128 rows, one a block)
   if (!cached_map(&mw_copy, W, (long long)groups * N, K, K, BM, true) || !cached_map(&mx_copy, X, M, K, ldx, 128, false))
     return refuse(ST_BAD_SIZE, "gemm_tcgen05_grouped: cuTensorMapEncodeTiled refused the operands");
+  if (tile_rows == 256) return launch_pair<256, 6>(mw, mx, a, 0, stream);
   return launch_persistent<128, 5>(mw, mx, a, 0, stream);
 }

@@ -120,7 +120,7 @@ class RoutedExperts(Part):
         s = self.spec
         T, H = x.shape
         ws = ctx.workspace
-        tile = ops.GROUPED_TILE
+        tile = ops.grouped_tile_rows(T * s.top, s.experts, 2 * s.intermediate_size * H)
         n_tiles = (T * s.top) // tile + s.experts            # every expert wastes less than one tile
         rows_cap = n_tiles * tile
         heads = ws.get("moe.heads", 2, s.experts + 1, torch.int32, reserve=2)
@@ -132,9 +132,10 @@ class RoutedExperts(Part):
         xs = ws.get("moe.xs", rows_cap, H, ctx.dtype, reserve=0)
         ops.moe_gather_rows(x, pair_of_row, s.top, xs)
         y = ws.get("moe.y_tiles", rows_cap, s.intermediate_size, ctx.dtype, reserve=0)
-        ops.gemm_tn_tcgen05_grouped(xs, self.gate_up, y, group_of_tile, glu=True, limit=s.limit, alpha=s.glu_alpha)
+        ops.gemm_tn_tcgen05_grouped(xs, self.gate_up, y, group_of_tile, glu=True, limit=s.limit, alpha=s.glu_alpha,
+                                    tile_rows=tile)
         rows = ws.get("moe.rows_tiles", rows_cap, H, torch.float32, reserve=0)
-        ops.gemm_tn_tcgen05_grouped(y, self.down, rows, group_of_tile)
+        ops.gemm_tn_tcgen05_grouped(y, self.down, rows, group_of_tile, tile_rows=tile)
         out = ws.get("moe.out", T, H, ctx.dtype)
         ops.moe_combine(rows, row_of_pair, weight, self._shared(ctx, first), out)
         return out

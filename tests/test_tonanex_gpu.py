@@ -599,9 +599,11 @@ def test_grouped_products_of_the_experts(dtype, interleaved):
         assert err < (2e-5 if dtype == torch.float32 else 2e-2), (T, E, top, float(err))
 
 
-def test_grouped_products_in_tiles_of_tensor_memory():
-    """Steps of many tokens: every expert's rows in whole tiles of 128 of a gathered copy, both products on the
-    persistent tensor-memory kernel.  An expert nobody chose, one with a single row, one with several tiles."""
+@pytest.mark.parametrize("tile", [128, 256])
+def test_grouped_products_in_tiles_of_tensor_memory(tile):
+    """Steps of many tokens: every expert's rows in whole tiles of 128 (one SM a tile) or 256 (a pair of SMs) of a
+    gathered copy, both products on the persistent tensor-memory kernel.  An expert nobody chose, one with a single
+    row, one with several tiles."""
     from safetyraise_lmengine_b200.kernels import ops
     dev = "cuda:0"
     g = torch.Generator().manual_seed(14)
@@ -617,7 +619,7 @@ def test_grouped_products_in_tiles_of_tensor_memory():
             choice[choice[:, 0] == 2, 0] = 0
             choice[7, 0] = 2                                    # expert 2: one row; expert 3: none; expert 4: many tiles
         weight = torch.rand(T, top, generator=g)
-        n, tile = T * top, ops.GROUPED_TILE
+        n = T * top
         n_tiles = n // tile + E
         d = lambda t: t.to(dev)
         heads = torch.zeros(2, E + 1, dtype=torch.int32, device=dev)
@@ -635,9 +637,9 @@ def test_grouped_products_in_tiles_of_tensor_memory():
         xs = torch.empty(n_tiles * tile, H, dtype=torch.bfloat16, device=dev)
         ops.moe_gather_rows(d(x), por, top, xs)
         y = torch.zeros(n_tiles * tile, ff, dtype=torch.bfloat16, device=dev)
-        ops.gemm_tn_tcgen05_grouped(xs, gu_dev, y, got, glu=True, limit=1.2, alpha=1.702)
+        ops.gemm_tn_tcgen05_grouped(xs, gu_dev, y, got, glu=True, limit=1.2, alpha=1.702, tile_rows=tile)
         rows = torch.zeros(n_tiles * tile, H, device=dev)
-        ops.gemm_tn_tcgen05_grouped(y, d(dn), rows, got)
+        ops.gemm_tn_tcgen05_grouped(y, d(dn), rows, got, tile_rows=tile)
         out = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
         ops.moe_combine(rows, rop, d(weight), None, out)
         assert ops.gemm_error_flag(torch.device(dev)) == 0
