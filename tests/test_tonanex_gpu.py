@@ -717,3 +717,56 @@ def test_command_line_and_trace_replay(tmp_path, tmp_path_factory):
     biggest = max(np.abs(ra).max(), np.abs(rb).max())
     for got, ref in ((read(0), ra[[0, 29]]), (read(1), ra[[31]]), (read(2), np.stack([rb[39], ra[49]]))):
         assert got.shape == ref.shape and np.abs(got - ref).max() <= TOL["float32"] * biggest
+
+
+# ---- configurations drawn at random: layer order, sizes and constants that no other test chose -----------------
+
+def random_config(seed):
+    rng = np.random.default_rng(2000 + seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]
+    width = pick(40, 64, 96, 128, 160)
+    layers = []
+    for i in range(int(rng.integers(2, 7))):
+        if layers and rng.random() < 0.3:
+            j = int(rng.integers(len(layers)))
+            layers.append(dict({k: v for k, v in layers[j].items() if k != "weights_of"}, weights_of=j))
+            continue
+        kv = pick(1, 2, 3)
+        dim, vdim = pick((8, 8), (16, 40), (24, 16), (32, 64), (64, 64), (128, 128), (48, 128), (80, 56))
+        kind = pick("dense", "moe", "moe", None)
+        if kind == "moe":
+            experts = pick(2, 3, 5, 8, 12)
+            mlp = moe(experts=experts, top=int(rng.integers(1, min(experts, 4) + 1)), ff=pick(8, 16, 24, 40, 50),
+                      limit=pick(0.8, 1.5, 3.0), shared=pick(0, 16, 36), shared_limit=pick(1.0, 2.5))
+        else:
+            mlp = {"kind": "dense", "ff": pick(32, 72, 100)} if kind else None
+        layers.append(attn(heads=kv * pick(1, 2, 4), kv_heads=kv, dim=dim, vdim=vdim, window=pick(None, 1, 9, 16, 50, 129, 1000),
+                           mlp=mlp))
+    return config(layers, width=width, vocab=pick(97, 160, 301), eps=pick(1e-6, 1e-5, 1e-4), softcap=pick(None, 5.0, 30.0))
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Whatever the order of layers and the sizes: float32 within the tolerance at every position under a cutting
+    with portions, decoded tokens and a second request beside it; bfloat16 by the rule of `check`."""
+    from safetyraise_lmengine_b200.weights.random_init import write_model_folder
+    from safetyraise_lmengine_b200.weights.safetensors_io import WeightFolder, write_safetensors
+    cfg = random_config(seed)
+    out = write_model_folder(cfg, 900 + seed, str(tmp_path / "m"))
+    src = WeightFolder(out)
+    W = sharpen({n: src.get(n).clone() for n in src.names()}, cfg, 50 + seed)
+    del src
+    write_safetensors(os.path.join(out, "model.safetensors"), W)
+    rng = np.random.default_rng(seed)
+    reqs = {"a": random_tokens(rng, 180, cfg["vocab"]), "b": random_tokens(rng, 37, cfg["vocab"])}
+    a, b = reqs["a"], reqs["b"]
+    steps = [{"entries": [("a", a[:61], list(range(61)))]},
+             {"entries": [("b", b[:2], [0, 1]), ("a", a[61:64], [0, 1, 2])]},
+             {"entries": [("a", a[64:150], list(range(86))), ("b", b[2:3], [0])]},
+             {"entries": [("b", b[3:36], list(range(33))), ("a", a[150:151], [0])]}]
+    steps += [{"entries": [("a", a[i:i + 1], [0])] + ([("b", b[36:], [0])] if i == 151 else [])} for i in range(151, 180)]
+    model = (f"random {seed}", out, cfg, W)
+    for dtype in DTYPES:
+        eng = build(out, dtype, num_pages=20, page_size=16)
+        check(replay(eng, steps), model, reqs, dtype)
+        assert all_pages_free(eng, 20)
